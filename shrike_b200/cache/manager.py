@@ -37,6 +37,7 @@ class KVGroupSpec:
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2   # tensors a token holds in a page: keys and values, or one that serves as both
 
 
 class IdPool:
@@ -277,6 +278,6 @@ def group_caches(needs: dict[int, object]) -> list[KVGroupSpec]:
     groups: dict[tuple, list[int]] = {}
     for cache_id in sorted(needs):
         need = needs[cache_id]
-        key = (need.num_kv_heads, need.head_dim, need.window)
+        key = (need.num_kv_heads, need.head_dim, need.window, getattr(need, "planes", 2))
         groups.setdefault(key, []).append(cache_id)
     return [KVGroupSpec(tuple(ids), *key) for key, ids in groups.items()]

@@ -1,7 +1,8 @@
 """Device memory behind the cache manager's ids.
 
 Each group of key/value caches is one tensor
-`[caches in group, 2, pages, page_size, kv heads, head size]` in the engine dtype:
+`[caches in group, planes, pages, page_size, kv heads, head size]` in the engine dtype (planes 2:
+keys and values; 1: one tensor a token that serves as both, a cached latent):
 the layout Azimml/shrike uses for its single pool
 (shrike/engine/model_runner.py:52-60, per layer viewed as pages at :74-75), once
 per group.  Per-request state of fixed size is one tensor `[slots, *shape]` per
@@ -17,7 +18,7 @@ from .manager import KVGroupSpec
 
 
 def page_bytes(group: KVGroupSpec, page_size: int, element_size: int) -> int:
-    return len(group.cache_ids) * 2 * page_size * group.num_kv_heads * group.head_dim * element_size
+    return len(group.cache_ids) * group.planes * page_size * group.num_kv_heads * group.head_dim * element_size
 
 
 def state_bytes(state_needs: dict, max_slots: int) -> int:
@@ -41,7 +42,7 @@ class CacheStorage:
         for index, (group, count) in enumerate(zip(self.groups, counts)):
             self.kv.append(
                 torch.zeros(
-                    len(group.cache_ids), 2, count, page_size, group.num_kv_heads, group.head_dim,
+                    len(group.cache_ids), group.planes, count, page_size, group.num_kv_heads, group.head_dim,
                     dtype=dtype, device=device,
                 )
             )
@@ -62,10 +63,11 @@ class CacheStorage:
             tensor.index_fill_(0, index, 0)
 
     def keys_values(self, cache_id: int):
-        """(group index, keys, values), each `[pages, page_size, kv heads, head size]`."""
+        """(group index, keys, values), each `[pages, page_size, kv heads, head size]`; in a group of one
+        plane both are the same tensor."""
         group, position = self.group_of_cache[cache_id]
         slab = self.kv[group][position]
-        return group, slab[0], slab[1]
+        return group, slab[0], slab[-1]
 
     def bytes(self) -> int:
         total = sum(t.numel() * t.element_size() for t in self.kv)

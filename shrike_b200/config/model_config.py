@@ -79,6 +79,75 @@ class AttentionSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class LayerNormSpec(PartSpec):
+    """Layer norm: (x - mean) / sqrt(var + eps) * weight (+ bias), var the mean squared deviation."""
+
+    width: int
+    eps: float
+    bias: bool = True
+    kind: str = field(init=False, default="layernorm")
+
+
+@dataclass(frozen=True)
+class SharedKeyValueAttentionSpec(PartSpec):
+    """Grouped-query softmax attention whose values are its keys: k = Wk x is stored twice, as
+    projected (the values) and normed (the keys); there is no value projection and no rotation.
+
+    `qk_norm`: q and k are each divided by their root mean square over the WHOLE projection (all
+    heads at once) and scaled by a weight of that size.  `q_temperature` (coef, every): the query
+    at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).  `softcap`: a score
+    s becomes softcap * tanh(s / softcap).  `slope_decay` d: head h (of H) takes
+    2^(-d (h + 1) / H) * (query position - key position) off its scores.  `window`: a query sees
+    only the `window` latest keys, itself included.  Each of these may be None (left out).
+    """
+
+    width: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    scale: float
+    eps: float
+    qk_norm: bool = True
+    q_temperature: tuple | None = None
+    softcap: float | None = None
+    slope_decay: float | None = None
+    window: int | None = None
+    kind: str = field(init=False, default="shared_kv_attention")
+
+    def __post_init__(self):
+        if self.num_heads % self.num_kv_heads:
+            raise ConfigError(f"heads={self.num_heads} is not a multiple of kv_heads={self.num_kv_heads}")
+        if self.window is not None and self.window < 1:
+            raise ConfigError(f"attention window must be >= 1, got {self.window}")
+        if self.softcap is not None and not self.softcap > 0:
+            raise ConfigError(f"softcap must be positive, got {self.softcap}")
+        if self.q_temperature is not None and self.q_temperature[1] < 1:
+            raise ConfigError(f"the query temperature's period must be >= 1, got {self.q_temperature[1]}")
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(PartSpec):
+    """Causal softmax attention over a cached low-rank latent, without positions.
+
+    c = RMS(Wdkv x) * weight is all that is cached (`latent_rank` numbers a token); head h's keys
+    and values are Wuk_h c and Wuv_h c.  `own_latent` False: the layer has no Wdkv and attends over
+    the latent another layer cached (the run order says whose).  `gated`: head h's output is
+    multiplied by sigmoid(Wg x)_h.
+    """
+
+    width: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    latent_rank: int
+    scale: float
+    eps: float
+    own_latent: bool = True
+    gated: bool = True
+    kind: str = field(init=False, default="latent_attention")
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
     """Dense gated feed-forward: down(act(gate(x)) * up(x)) (shrike/models/qwen.py:128-136)."""
 
@@ -95,6 +164,16 @@ class TokenEmbeddingSpec(PartSpec):
     vocab: int
     width: int
     kind: str = field(init=False, default="token_embedding")
+
+
+@dataclass(frozen=True)
+class TokenPositionEmbeddingSpec(PartSpec):
+    """A table row per token id plus a learned vector per position (not scaled), summed in 32-bit."""
+
+    vocab: int
+    width: int
+    max_positions: int
+    kind: str = field(init=False, default="token_position_embedding")
 
 
 @dataclass(frozen=True)
@@ -128,15 +207,17 @@ class LayerSpec:
 
     mixer: PartSpec
     mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward: PartSpec | None
+    feed_forward_norm: PartSpec | None
     block: str = "pre_norm"
     extra: tuple = ()
 
     def roles(self):
-        """(role, category, spec) of every part of the layer."""
+        """(role, category, spec) of every part of the layer; a part the layer leaves out (None, where
+        its block allows that: a layer without a feed-forward) is not listed."""
         for role, category in STANDARD_ROLES:
-            yield role, category, getattr(self, role)
+            if getattr(self, role) is not None:
+                yield role, category, getattr(self, role)
         yield from self.extra
 
 

@@ -35,12 +35,26 @@ class TensorNames:
     layer_part: Callable[[int, str], str]
     embedding_prefix: str | None = None
     head_prefix: str | None = None
+    # (role, a part's own parameter name) -> the name's last piece in this architecture's files; None:
+    # the part's own names are the files' names.  Roles: a layer's roles, "final_norm", "embedding", "head".
+    local_name: Callable[[str, str], str] | None = None
+
+    def local(self, role: str, local: str) -> str:
+        return local if self.local_name is None else self.local_name(role, local)
+
+    def layer_tensor(self, layer: int, role: str, local: str) -> str:
+        return self.layer_part(layer, role) + self.local(role, local)
+
+    def final_norm_name(self, local: str) -> str:
+        return self.final_norm_prefix + self.local("final_norm", local)
 
     def embedding_name(self, local: str) -> str:
-        return self.embedding if local == "weight" else _prefix(self.embedding_prefix, self.embedding) + local
+        if local == "weight":
+            return self.embedding
+        return _prefix(self.embedding_prefix, self.embedding) + self.local("embedding", local)
 
     def head_name(self, local: str) -> str:
-        return self.lm_head if local == "weight" else _prefix(self.head_prefix, self.lm_head) + local
+        return self.lm_head if local == "weight" else _prefix(self.head_prefix, self.lm_head) + self.local("head", local)
 
 
 def _prefix(given: str | None, weight_name: str) -> str:
@@ -72,6 +86,8 @@ def _register_builtin() -> None:
 def architecture_of(raw: dict) -> Architecture:
     _register_builtin()
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):   # some configurations name it in the singular
+        names = [raw["architecture"]]
     if not names or not isinstance(names, list):
         raise ConfigError(
             "config.json lacks `architectures`; known: " + ", ".join(sorted(ARCHITECTURES))

@@ -98,7 +98,23 @@ struct Params {
   int* status;          // host-visible; a wait that ran out leaves ERR_TILE_WAIT here
   int skip_single;      // portions kernel: leave q_len == 1 to the single-token kernel
   float scale_log2;     // scale * log2(e)
+  // optional changes to a score s = scale * q.k, in this order (both off: softcap 0, slopes null):
+  float scale;          //   the plain scale, for the two below
+  float softcap;        //   s <- softcap * tanh(s / softcap)
+  const float* slopes;  //   s <- s - slopes[head] * (query position - key position)
 };
+
+// A score as the softmax takes it (times log2 e), with the soft cap and the distance bias.  The
+// hyperbolic tangent is 1 - 2 / (exp(2 x) + 1) with the hardware exponential: absolute error
+// about 1e-7, far below what bfloat16 queries and keys leave in a score.
+__device__ __forceinline__ float modified_score(float dot, float scale, float softcap, float slope, int distance) {
+  float s = dot * scale;
+  if (softcap > 0.f) {
+    const float x = __fdividef(s, softcap);
+    s = softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f));
+  }
+  return (s - slope * static_cast<float>(distance)) * LOG2E;
+}
 
 // Where the keys [tile_base, tile_base + BN) of one kv head start in the cache, in
 // elements; -1 for keys outside [lo, hi] or on a page the sequence does not hold.  One
@@ -211,7 +227,8 @@ __device__ __forceinline__ void accumulate(float (&o)[DTILES][4], const float (&
 template <int NT>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[DTILES][4], float (&row_max)[2],
                                                float (&row_sum)[2], const int (&first)[2], const int (&last)[2],
-                                               int key_base, float scale_log2, int lane) {
+                                               int key_base, float scale_log2, int lane, bool modified = false,
+                                               float scale = 0.f, float softcap = 0.f, float slope = 0.f) {
   float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
   for (int j = 0; j < NT; ++j)
@@ -220,7 +237,8 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[DTI
       const int key = key_base + j * 8 + (lane & 3) * 2 + (e & 1);
       const int r = e >> 1;
       const bool seen = key >= first[r] && key <= last[r];
-      s[j][e] = seen ? s[j][e] * scale_log2 : -INFINITY;
+      const float value = modified ? modified_score(s[j][e], scale, softcap, slope, last[r] - key) : s[j][e] * scale_log2;
+      s[j][e] = seen ? value : -INFINITY;
       tile_max[r] = fmaxf(tile_max[r], s[j][e]);
     }
   float correction[2], base[2];
@@ -296,6 +314,8 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+  const bool modified = p.softcap > 0.f || p.slopes != nullptr;
+  const float slope = p.slopes != nullptr ? p.slopes[head] : 0.f;
   unsigned q_frag[1][4];   // query fragments are re-read from shared memory: registers are the scarcer resource here
   const bf16* q_rows = q_tile + warp * 16 * ROW;
 
@@ -322,7 +342,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
       const bf16* k_tile = k_tiles + buffer * PBN * ROW;
       const bf16* v_tile = v_tiles + buffer * PBN * ROW;
       scores<PBN / 8, false>(s, q_frag, q_rows, k_tile, 0, lane);
-      softmax_update<PBN / 8>(s, o, row_max, row_sum, first, last, tile * PBN, p.scale_log2, lane);
+      softmax_update<PBN / 8>(s, o, row_max, row_sum, first, last, tile * PBN, p.scale_log2, lane, modified, p.scale, p.softcap, slope);
       accumulate<PBN / 8>(o, s, v_tile, 0, lane);
     }
     __syncthreads();
@@ -438,6 +458,15 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       for (int e = 0; e < 4; ++e) o[i][j][e] = 0.f;
   float row_max[2] = {-INFINITY, -INFINITY};   // the same in every warp
   float row_sum[2] = {0.f, 0.f};               // this thread's share: its keys only
+  const bool modified = p.softcap > 0.f || p.slopes != nullptr;
+  float slope[2] = {0.f, 0.f};                 // of the heads in rows lane/4 and lane/4 + 8
+  if (p.slopes != nullptr) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = (lane >> 2) + 8 * r;
+      if (row < rows_here) slope[r] = p.slopes[head0 + row];
+    }
+  }
 
   // PAGES: the ninth warp brings the tiles in.  Its lane j looks up page j of a tile in the block
   // table (-1: no key of [first_key, last_key] lies there, or the sequence holds no such page);
@@ -612,7 +641,9 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       for (int e = 0; e < 4; ++e) {
         const int key = tile * BN + key0 + (lane & 3) * 2 + (e & 1);
         const bool seen = key >= first_key && key <= last_key;
-        sc[e] = seen ? sc[e] * p.scale_log2 : -INFINITY;
+        const float value = modified ? modified_score(sc[e], p.scale, p.softcap, slope[e >> 1], last_key - key)
+                                     : sc[e] * p.scale_log2;
+        sc[e] = seen ? value : -INFINITY;
         tile_max[e >> 1] = fmaxf(tile_max[e >> 1], sc[e]);
       }
 #pragma unroll
@@ -882,12 +913,15 @@ SHRIKE_API int shrike_attention_bf16_resident_ctas() {
 // shrike_attention_bf16_scratch_floats(num_seqs, num_heads, splits, cluster) floats when has_single, and
 // arrivals num_seqs * num_kv_heads * ceil(group / 16) ints that are zero before the first launch
 // (every launch leaves them zero again).
-SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, const void* v_cache,
-                                           const int* block_table, int max_blocks, const int* q_start,
-                                           const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
-                                           int page_size, int num_pages, float scale, int window, void* out,
-                                           int has_single, int has_portions, int max_q_len, int splits,
-                                           int cluster, float* scratch, int* arrivals, int* status, cudaStream_t stream) {
+// `softcap` > 0 and `slopes` (float32 [num_heads], or null) change a score s = scale * q.k to
+// softcap * tanh(s / softcap) and then to s - slopes[head] * (query position - key position).
+SHRIKE_API int shrike_paged_attention_bf16_scores(const void* q, const void* k_cache, const void* v_cache,
+                                                  const int* block_table, int max_blocks, const int* q_start,
+                                                  const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
+                                                  int page_size, int num_pages, float scale, int window, void* out,
+                                                  int has_single, int has_portions, int max_q_len, int splits,
+                                                  int cluster, float* scratch, int* arrivals, int* status,
+                                                  float softcap, const float* slopes, cudaStream_t stream) {
   using namespace bf16attn;
   if (num_seqs <= 0) return SHRIKE_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0 ||
@@ -930,6 +964,9 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
   p.cluster = has_single ? cluster : 1;
   p.skip_single = has_single ? 1 : 0;
   p.scale_log2 = scale * LOG2E;
+  p.scale = scale;
+  p.softcap = softcap > 0.f ? softcap : 0.f;
+  p.slopes = slopes;
   p.partial_out = scratch;
   p.partial_ml = scratch ? scratch + static_cast<size_t>(num_seqs) * num_heads * (p.splits / p.cluster) * D : nullptr;
   p.arrivals = arrivals;
@@ -952,4 +989,16 @@ SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, c
     launch_dependent(portions_kernel, grid, THREADS, PORTIONS_SMEM, stream, p);
   }
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int max_blocks, const int* q_start,
+                                           const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
+                                           int page_size, int num_pages, float scale, int window, void* out,
+                                           int has_single, int has_portions, int max_q_len, int splits,
+                                           int cluster, float* scratch, int* arrivals, int* status, cudaStream_t stream) {
+  return shrike_paged_attention_bf16_scores(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, num_seqs,
+                                            num_heads, num_kv_heads, page_size, num_pages, scale, window, out, has_single,
+                                            has_portions, max_q_len, splits, cluster, scratch, arrivals, status, 0.f,
+                                            nullptr, stream);
 }

@@ -8,6 +8,8 @@
 // maximum and sum.  Key j of a sequence lives in page table[j / page_size], row
 // j % page_size.  The work for one (token, head) does not depend on what else is
 // in the batch, so results are the same however requests are cut or mixed.
+// Two optional changes to a score s = scale * q.k, in this order: a soft cap, s <- cap * tanh(s / cap)
+// (softcap > 0), and a distance bias, s <- s - slopes[head] * (p - j) for key j (slopes != null).
 //
 // Built once per head size: -DSHRIKE_HEAD_DIM=<multiple of 16, at most 256>.
 #include "common.cuh"
@@ -51,7 +53,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                int max_blocks, const int* __restrict__ q_start,
                                const int* __restrict__ ctx_len, const int* __restrict__ seq_of_token,
                                int num_heads, int num_kv_heads, int page_size, int num_pages,
-                               float scale, int window, T* __restrict__ out, int num_tokens) {
+                               float scale, int window, float softcap, const float* __restrict__ slopes,
+                               T* __restrict__ out, int num_tokens) {
   __shared__ float q_shared[WARPS][D];
   let_dependents_start();
   wait_for_previous();
@@ -67,6 +70,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   const int last = ctx_len[seq] - q_len + (token - start);
   const int first = window > 0 ? max(0, last - window + 1) : 0;
   const int* table = block_table + static_cast<size_t>(seq) * max_blocks;
+  const float slope = slopes != nullptr ? slopes[head] : 0.f;
 
   const T* q_row = q + (static_cast<size_t>(token) * num_heads + head) * D;
   for (int d = lane; d < D; d += 32) q_shared[warp][d] = to_float(q_row[d]);
@@ -99,6 +103,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
         for (int i = 0; i < 16; ++i) dot = fmaf(q_shared[warp][c * 16 + i], chunk.get(i), dot);
       }
       score = dot * scale;
+      if (softcap > 0.f) score = softcap * tanhf(score / softcap);
+      if (slopes != nullptr) score -= slope * static_cast<float>(last - key);
     }
     const float tile_max = warp_max(score);
     const float new_max = fmaxf(running_max, tile_max);
@@ -138,7 +144,7 @@ SHRIKE_API int shrike_paged_attention_generic(const void* q, const void* k_cache
                                               const int* ctx_len, const int* seq_of_token, int dtype,
                                               int num_tokens, int num_heads, int num_kv_heads,
                                               int page_size, int num_pages, float scale, int window,
-                                              void* out, cudaStream_t stream) {
+                                              float softcap, const float* slopes, void* out, cudaStream_t stream) {
   if (num_tokens <= 0) return SHRIKE_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0)
     return SHRIKE_BAD_ARGUMENT;
@@ -149,7 +155,7 @@ SHRIKE_API int shrike_paged_attention_generic(const void* q, const void* k_cache
   paged_attention_generic_kernel<T><<<static_cast<int>(blocks), WARPS * 32, 0, stream>>>(           \
       static_cast<const T*>(q), static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),     \
       block_table, max_blocks, q_start, ctx_len, seq_of_token, num_heads, num_kv_heads, page_size,  \
-      num_pages, scale, window, static_cast<T*>(out), num_tokens)
+      num_pages, scale, window, softcap, slopes, static_cast<T*>(out), num_tokens)
   if (dtype == SHRIKE_F32) SHRIKE_ATTN_CASE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_ATTN_CASE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;

@@ -111,6 +111,26 @@ template <> __device__ __forceinline__ float silu_times<__nv_bfloat16>(float g, 
   return __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), u);
 }
 
+// gelu_tanh(g) * u, gelu_tanh(g) = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))), with one rounding
+// of the product.  As with SiLU, the bfloat16 path may use the hardware exponential
+// (tanh(z) = 1 - 2 / (exp(2 z) + 1)); the float32 path uses tanhf.
+template <typename T> __device__ __forceinline__ float gelu_tanh_times(float g, float u);
+template <> __device__ __forceinline__ float gelu_tanh_times<float>(float g, float u) {
+  const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+  return __fmul_rn(0.5f * g * (1.0f + tanhf(z)), u);
+}
+template <> __device__ __forceinline__ float gelu_tanh_times<__nv_bfloat16>(float g, float u) {
+  const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+  const float t = 1.0f - __fdividef(2.0f, __expf(2.0f * z) + 1.0f);
+  return __fmul_rn(0.5f * g * (1.0f + t), u);
+}
+
+// Activation codes of the gated feed-forward, shared with the Python side.
+enum : int { SHRIKE_ACT_SILU = 0, SHRIKE_ACT_GELU_TANH = 1 };
+template <typename T> __device__ __forceinline__ float act_times(int act, float g, float u) {
+  return act == SHRIKE_ACT_GELU_TANH ? gelu_tanh_times<T>(g, u) : silu_times<T>(g, u);
+}
+
 // base[0] + base[stride] + ... over `partials` slices (the stack a K-split product leaves),
 // added in ascending order.  Up to 16 loads are issued together before the first addition,
 // so the sum costs one memory latency, not one per slice.

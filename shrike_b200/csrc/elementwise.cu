@@ -9,10 +9,13 @@
 // A negative id -1 - r stands for "the token the step before drew in its row r": it is read
 // from `previous` on the device, so that a step can be launched before the host has seen the
 // tokens of the step before it.  Ids outside the vocabulary give a row of zeros.
+// With `pos_table` (a learned vector per position, [max_positions, width]) the row of the token's
+// position is added in float32; a position outside the table adds nothing.
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int width, int vocab,
-                             const int* __restrict__ previous, int previous_rows) {
+                             const int* __restrict__ previous, int previous_rows,
+                             const T* __restrict__ pos_table, const int* __restrict__ positions, int max_positions) {
   let_dependents_start();
   wait_for_previous();
   const int row = blockIdx.x;
@@ -22,23 +25,42 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
   if (!valid) id = 0;
   const T* src = table + static_cast<size_t>(id) * width;
   float* dst = out + static_cast<size_t>(row) * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = valid ? to_float(src[i]) : 0.f;
+  const T* pos_row = nullptr;
+  if (pos_table != nullptr) {
+    const int p = positions[row];
+    if (p >= 0 && p < max_positions) pos_row = pos_table + static_cast<size_t>(p) * width;
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = valid ? to_float(src[i]) : 0.f;
+    if (pos_row != nullptr) v = __fadd_rn(v, to_float(pos_row[i]));
+    dst[i] = v;
+  }
+}
+
+// `pos_table` (same type as `table`) and `positions` may be null: a plain token embedding.
+SHRIKE_API int shrike_embed_positions(const int* ids, const void* table, int table_dtype, float* out, int n,
+                                      int width, int vocab, const int* previous, int previous_rows,
+                                      const void* pos_table, const int* positions, int max_positions,
+                                      cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (width <= 0 || vocab <= 0) return SHRIKE_BAD_ARGUMENT;
+  if (pos_table != nullptr && (positions == nullptr || max_positions <= 0)) return SHRIKE_BAD_ARGUMENT;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (table_dtype == SHRIKE_F32)
+    launch_dependent(embed_kernel<float>, n, threads, 0, stream, ids, static_cast<const float*>(table), out, width, vocab,
+                     previous, previous_rows, static_cast<const float*>(pos_table), positions, max_positions);
+  else if (table_dtype == SHRIKE_BF16)
+    launch_dependent(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, ids, static_cast<const __nv_bfloat16*>(table), out, width,
+                     vocab, previous, previous_rows, static_cast<const __nv_bfloat16*>(pos_table), positions, max_positions);
+  else
+    return SHRIKE_BAD_ARGUMENT;
+  return shrike_launch_status();
 }
 
 SHRIKE_API int shrike_embed(const int* ids, const void* table, int table_dtype, float* out, int n,
                             int width, int vocab, const int* previous, int previous_rows, cudaStream_t stream) {
-  if (n <= 0) return SHRIKE_OK;
-  if (width <= 0 || vocab <= 0) return SHRIKE_BAD_ARGUMENT;
-  const int threads = width >= 1024 ? 256 : 128;
-  if (table_dtype == SHRIKE_F32)
-    launch_dependent(embed_kernel<float>, n, threads, 0, stream, ids, static_cast<const float*>(table), out, width, vocab,
-                     previous, previous_rows);
-  else if (table_dtype == SHRIKE_BF16)
-    launch_dependent(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, ids, static_cast<const __nv_bfloat16*>(table), out, width,
-                     vocab, previous, previous_rows);
-  else
-    return SHRIKE_BAD_ARGUMENT;
-  return shrike_launch_status();
+  return shrike_embed_positions(ids, table, table_dtype, out, n, width, vocab, previous, previous_rows, nullptr, nullptr, 0,
+                                stream);
 }
 
 // ------------------------------------------------- residual add + RMSNorm
@@ -247,7 +269,7 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
 // (the order in which a fused gate/up matrix keeps its rows for the tensor-core product's own
 // activation epilogue); b is a multiple of VEC.
 template <typename T, int VEC>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int rows, int block) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int rows, int block, int act) {
   let_dependents_start();
   wait_for_previous();
   // blockIdx.y walks the rows, blockIdx.x and the threads a row's groups of VEC columns: no division
@@ -278,7 +300,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
         if (group >= groups_per_row) continue;
         Pack r;
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(silu_times<T>(to_float(g[k].v[j]), to_float(u[k].v[j])));
+        for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(act_times<T>(act, to_float(g[k].v[j]), to_float(u[k].v[j])));
         *reinterpret_cast<Pack*>(out_row + group * VEC) = r;
       }
     }
@@ -316,8 +338,8 @@ __global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up
 }
 
 template <typename T>
-static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, int block, cudaStream_t stream) {
-  if (sizeof(T) == 2 && block == 16 && inter % 16 == 0 &&
+static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, int block, int act, cudaStream_t stream) {
+  if (act == SHRIKE_ACT_SILU && sizeof(T) == 2 && block == 16 && inter % 16 == 0 &&
       (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
     const int threads = 256, runs_per_row = inter / 16;
     const dim3 grid(max(1, min(64, (runs_per_row + threads - 1) / threads)), max(1, min(n, 65535)));
@@ -336,19 +358,26 @@ static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, in
   const dim3 grid(across, down);
   if (vec)
     launch_dependent(silu_mul_kernel<T, WIDE>, grid, threads, 0, stream, static_cast<const T*>(gate_up),
-                     static_cast<T*>(out), inter, n, block);
+                     static_cast<T*>(out), inter, n, block, act);
   else
     launch_dependent(silu_mul_kernel<T, 1>, grid, threads, 0, stream, static_cast<const T*>(gate_up),
-                     static_cast<T*>(out), inter, n, block);
+                     static_cast<T*>(out), inter, n, block, act);
+}
+
+// out = act(gate) * up with `act` one of SHRIKE_ACT_*; the layout of gate_up as for shrike_silu_mul.
+SHRIKE_API int shrike_act_mul(const void* gate_up, void* out, int dtype, int n, int inter, int block, int act,
+                              cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (inter <= 0 || block < 0 || (block > 0 && inter % block)) return SHRIKE_BAD_ARGUMENT;
+  if (act != SHRIKE_ACT_SILU && act != SHRIKE_ACT_GELU_TANH) return SHRIKE_BAD_ARGUMENT;
+  if (dtype == SHRIKE_F32) launch_silu_mul<float>(gate_up, out, n, inter, block, act, stream);
+  else if (dtype == SHRIKE_BF16) launch_silu_mul<__nv_bfloat16>(gate_up, out, n, inter, block, act, stream);
+  else return SHRIKE_BAD_ARGUMENT;
+  return shrike_launch_status();
 }
 
 SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, int block, cudaStream_t stream) {
-  if (n <= 0) return SHRIKE_OK;
-  if (inter <= 0 || block < 0 || (block > 0 && inter % block)) return SHRIKE_BAD_ARGUMENT;
-  if (dtype == SHRIKE_F32) launch_silu_mul<float>(gate_up, out, n, inter, block, stream);
-  else if (dtype == SHRIKE_BF16) launch_silu_mul<__nv_bfloat16>(gate_up, out, n, inter, block, stream);
-  else return SHRIKE_BAD_ARGUMENT;
-  return shrike_launch_status();
+  return shrike_act_mul(gate_up, out, dtype, n, inter, block, SHRIKE_ACT_SILU, stream);
 }
 
 // --------------------------------------- bias + rotary + key/value store

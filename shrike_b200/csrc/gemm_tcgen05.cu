@@ -68,8 +68,8 @@ struct Args {
   int* status;          // host-visible; first failing role is recorded
   int tokens, n, k, tn; // tn: token columns of the MMA (multiple of 16, at most 256)
   int kblocks_per_split, stages, out_dtype;
-  int gated;            // the weight rows come in runs of 16 gate rows and the 16 up rows of the same
-                        // features; out is [T][N / 2] bfloat16 = silu(gate) * up
+  int gated;            // nonzero (1 + activation code): the weight rows come in runs of 16 gate rows and the 16 up
+                        // rows of the same features; out is [T][N / 2] bfloat16 = act(gate) * up
 };
 
 __global__ void __launch_bounds__(THREADS, 3)
@@ -199,7 +199,7 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const int t = t0 + c0 + j + (lane < 16 ? 0 : 8);
           if (t < args.tokens && n0 + quarter * 32 + lane < args.n)
             static_cast<__nv_bfloat16*>(args.out)[static_cast<size_t>(t) * half_n + feature] =
-                __float2bfloat16_rn(silu_times<__nv_bfloat16>(gate, up));
+                __float2bfloat16_rn(act_times<__nv_bfloat16>(args.gated - 1, gate, up));
         }
       }
     } else if (ok) {
@@ -340,4 +340,11 @@ SHRIKE_API int shrike_gemm_tc_gated(const void* x, const void* w, void* out, int
                                     cudaStream_t stream) {
   if (n % 32) return SHRIKE_BAD_ARGUMENT;
   return launch_gemm_tc(x, w, nullptr, out, SHRIKE_BF16, tokens, n, k, 1, 1, status, stream);
+}
+
+// The same with the activation named: act(x w_gate^T) * (x w_up^T), `act` one of SHRIKE_ACT_*.
+SHRIKE_API int shrike_gemm_tc_gated_act(const void* x, const void* w, void* out, int tokens, int n, int k, int act,
+                                        int* status, cudaStream_t stream) {
+  if (n % 32 || (act != SHRIKE_ACT_SILU && act != SHRIKE_ACT_GELU_TANH)) return SHRIKE_BAD_ARGUMENT;
+  return launch_gemm_tc(x, w, nullptr, out, SHRIKE_BF16, tokens, n, k, 1, 1 + act, status, stream);
 }

@@ -64,6 +64,7 @@ class StepContext:
     sample_top_p: torch.Tensor | None = None  # float32 [R]
     sample_seed: torch.Tensor | None = None  # int64 [R]
     previous_tokens: torch.Tensor | None = None  # int32: what the step before drew; an id of -1 - r means its row r
+    carried: dict = field(default_factory=dict)  # what one part leaves for the next within this forward pass
 
 
 @dataclass

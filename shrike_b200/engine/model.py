@@ -57,10 +57,6 @@ class Runtime:
         return sum(t.numel() * t.element_size() for t in self._buffers.values())
 
 
-def _take(tensors: dict, prefix: str, names) -> dict:
-    return {local: tensors[prefix + local] for local in names}
-
-
 class DecoderModel:
     def __init__(self, config: ModelConfig, tensors: dict[str, torch.Tensor], ops, runtime: Runtime):
         self.config = config
@@ -77,14 +73,16 @@ class DecoderModel:
             built = {}
             for role, category, spec in layer.roles():
                 cls = part_class(category, spec.kind)
-                built[role] = cls(spec, _take(tensors, names.layer_part(index, role), cls.parameters(spec)), ops, runtime)
+                built[role] = cls(spec, {local: tensors[names.layer_tensor(index, role, local)]
+                                         for local in cls.parameters(spec)}, ops, runtime)
             self.blocks.append(part_class("block", layer.block)(**built))
             if hasattr(self.blocks[-1], "prepare"):
                 self.blocks[-1].prepare()
             parts += [*built.values(), self.blocks[-1]]
         norm = config.final_norm
         cls = part_class("norm", norm.kind)
-        self.final_norm = cls(norm, _take(tensors, names.final_norm_prefix, cls.parameters(norm)), ops, runtime)
+        self.final_norm = cls(norm, {local: tensors[names.final_norm_name(local)] for local in cls.parameters(norm)},
+                              ops, runtime)
         spec = config.head
         cls = part_class("head", spec.kind)
         local_tensors = {}
@@ -137,6 +135,7 @@ class DecoderModel:
 
     def forward(self, ctx) -> torch.Tensor:
         """float32 logits [R, vocab] at `ctx.out_rows`."""
+        ctx.carried.clear()   # nothing is carried from one forward pass to the next
         resid = self.embedding.forward(ctx)
         delta = None
         for run in self.config.order:

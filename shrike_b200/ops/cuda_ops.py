@@ -95,6 +95,8 @@ class CudaOps:
             self.gemm_tc.shrike_gemm_tc.restype = _I
             self.gemm_tc.shrike_gemm_tc_gated.argtypes = [_P, _P, _P, _I, _I, _I, _P, _P]
             self.gemm_tc.shrike_gemm_tc_gated.restype = _I
+            self.gemm_tc.shrike_gemm_tc_gated_act.argtypes = [_P, _P, _P, _I, _I, _I, _I, _P, _P]
+            self.gemm_tc.shrike_gemm_tc_gated_act.restype = _I
             self.gemm_tc.shrike_gemm_tc_splits.argtypes = [_I, _I, _I]
             self.gemm_tc.shrike_gemm_tc_splits.restype = _I
         self._scratch = None     # partial results of split single-token attention
@@ -124,10 +126,19 @@ class CudaOps:
         lib.shrike_kv_write.argtypes = [_P] * 5 + [_I, _I, _I, _LL, _P]
         lib.shrike_gemm_fp32.argtypes = [_P, _P, _P, _P, _I, _I, _I, _P]
         lib.shrike_sample.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P]
+        lib.shrike_embed_positions.argtypes = [_P, _P, _I, _P, _I, _I, _I, _P, _I, _P, _P, _I, _P]
+        lib.shrike_act_mul.argtypes = [_P, _P, _I, _I, _I, _I, _I, _P]
+        lib.shrike_norm_rows.argtypes = [_P, _P, _I, _I, _LL, _P, _P, _P, _F, _I, _P, _I, _I, _I, _P]
+        lib.shrike_qk_norm_store.argtypes = [_P, _I, _LL, _P, _P, _F, _P, _F, _I, _P, _P, _P, _P] + [_I] * 6 + [_LL, _P]
+        lib.shrike_latent_store.argtypes = [_P, _I, _LL, _P, _F, _P, _P, _P, _P] + [_I] * 6 + [_LL, _P]
+        lib.shrike_head_scale.argtypes = [_P, _P, _I, _I, _I, _I, _P]
+        lib.shrike_gemm_fp32_heads.argtypes = [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _P]
         lib.shrike_sample_slices.argtypes = [_I]
         lib.shrike_sample_slices.restype = _I
         for name in ("shrike_embed", "shrike_add_rmsnorm", "shrike_silu_mul", "shrike_rope_kv_write",
-                     "shrike_kv_write", "shrike_gemm_fp32", "shrike_sample"):
+                     "shrike_kv_write", "shrike_gemm_fp32", "shrike_sample", "shrike_embed_positions", "shrike_act_mul",
+                     "shrike_norm_rows", "shrike_qk_norm_store", "shrike_latent_store", "shrike_head_scale",
+                     "shrike_gemm_fp32_heads"):
             getattr(lib, name).restype = _I
 
     def _attention_lib(self, head_dim: int):
@@ -136,13 +147,17 @@ class CudaOps:
             self.check_head_dim(head_dim)
             lib = build.attention_library(head_dim)
             lib.shrike_paged_attention_generic.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _P, _P]
+                [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _F, _P, _P, _P]
             )
             lib.shrike_paged_attention_generic.restype = _I
             lib.shrike_paged_attention_bf16.argtypes = (
                 [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _P]
             )
             lib.shrike_paged_attention_bf16.restype = _I
+            lib.shrike_paged_attention_bf16_scores.argtypes = (
+                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _F, _P, _P]
+            )
+            lib.shrike_paged_attention_bf16_scores.restype = _I
             lib.shrike_attention_single_token_pages.argtypes = [_I]
             lib.shrike_attention_single_token_pages.restype = None
             lib.shrike_attention_bf16_resident_ctas.restype = _I
@@ -185,18 +200,25 @@ class CudaOps:
         return self._layer_program
 
     # ---- kernels ------------------------------------------------------------
-    def embed(self, ids, table, out, previous=None):
+    def embed(self, ids, table, out, previous=None, position_table=None, positions=None):
         """Rows of `table` into the float32 residual.  An id of -1 - r is replaced on the device
-        by `previous[r]` (int32: the tokens the step before drew)."""
+        by `previous[r]` (int32: the tokens the step before drew).  With `position_table`
+        ([max positions, width], the type of `table`) the row of each token's position is added."""
         _dense(ids, torch.int32, "token ids")
         _dense(out, torch.float32, "residual")
         n, width = out.shape
         if previous is not None:
             _dense(previous, torch.int32, "previous tokens")
+        if position_table is not None:
+            _dense(position_table, table.dtype, "position table")
+            _dense(positions, torch.int32, "positions")
+            if position_table.shape[1] != width:
+                raise KernelError("the position table's rows must be as wide as the residual")
         self.launches += 1
-        _check(self.core.shrike_embed(_ptr(ids), _ptr(table), _DTYPE_CODE[table.dtype], _ptr(out), n, width,
-                                      table.shape[0], _ptr(previous), 0 if previous is None else previous.numel(),
-                                      self._stream()), "embed")
+        _check(self.core.shrike_embed_positions(
+            _ptr(ids), _ptr(table), _DTYPE_CODE[table.dtype], _ptr(out), n, width, table.shape[0], _ptr(previous),
+            0 if previous is None else previous.numel(), _ptr(position_table), _ptr(positions),
+            0 if position_table is None else position_table.shape[0], self._stream()), "embed")
 
     @staticmethod
     def _stack(delta):
@@ -227,6 +249,97 @@ class CudaOps:
         _check(self.core.shrike_add_rmsnorm(_ptr(resid), _ptr(delta), code, _ptr(rows), _ptr(weight), eps,
                                             _ptr(out), _DTYPE_CODE[out.dtype], rows.shape[0], width, partials,
                                             stride, self._stream()), "gather_add_rmsnorm")
+
+    def norm_add(self, resid, branch, weight, bias, eps, out, layer_norm=True):
+        """resid += norm(branch) (float32 sum), for a branch [N, W] or a [P, N, W] stack of partial sums;
+        `out` (may be None) gets the new residual in its own type.  `branch` None: only that cast.
+        norm: layer norm with the variance as the mean squared deviation (`layer_norm`), else RMS."""
+        _dense(resid, torch.float32, "residual")
+        n, width = resid.shape
+        code = -1 if branch is None else _DTYPE_CODE[branch.dtype]
+        partials, stride = self._stack(branch)
+        self.launches += 1
+        _check(self.core.shrike_norm_rows(
+            _ptr(resid), _ptr(branch), code, partials, stride, None, _ptr(weight), _ptr(bias), eps, int(layer_norm),
+            _ptr(out), -1 if out is None else _DTYPE_CODE[out.dtype], n, width, self._stream()), "norm_add")
+
+    def gather_norm(self, resid, rows, weight, bias, eps, out, layer_norm=True):
+        """out[r] = norm(resid[rows[r]]): the final norm on the wanted rows only."""
+        _dense(resid, torch.float32, "residual")
+        _dense(rows, torch.int32, "rows")
+        self.launches += 1
+        _check(self.core.shrike_norm_rows(
+            _ptr(resid), None, -1, 1, 0, _ptr(rows), _ptr(weight), _ptr(bias), eps, int(layer_norm),
+            _ptr(out), _DTYPE_CODE[out.dtype], rows.shape[0], resid.shape[1], self._stream()), "gather_norm")
+
+    def qk_norm_store(self, qk, q_weight, k_weight, eps, positions, temperature, q_out, keys, values, slots,
+                      num_heads, num_kv_heads, dim, padded):
+        """Queries and keys of a fused q|k projection ([N, (H + G) D] float32 or a K-split stack): each
+        divided by its root mean square over the WHOLE projection and scaled by its weight (None: left
+        as projected), the query times 1 + coef * ln(floor((p + 1) / every) + 1) for `temperature`
+        (coef, every) at position p; queries to `q_out` [N, H * padded], keys to the key pages and the
+        keys as projected to the value pages, heads `padded` elements apart (padding zeroed)."""
+        _dense(qk, torch.float32, "q|k projection")
+        _dense(q_out, self.dtype, "q")
+        partials, stride = self._stack(qk)
+        num_slots = 0
+        if keys is not None:
+            _dense(keys, self.dtype, "key cache")
+            _dense(values, self.dtype, "value cache")
+            num_slots = keys.shape[0] * keys.shape[1]
+        coef, every = temperature if temperature is not None else (0.0, 0)
+        self.launches += 1
+        _check(self.core.shrike_qk_norm_store(
+            _ptr(qk), partials, stride, _ptr(q_weight), _ptr(k_weight), eps, _ptr(positions), coef, every, _ptr(q_out),
+            _ptr(keys), _ptr(values), _ptr(slots), self.code, qk.shape[-2], num_heads, num_kv_heads, dim, padded,
+            num_slots, self._stream()), "qk_norm_store")
+
+    def latent_store(self, fused, latent_weight, eps, q_out, latents, slots, gate_out, q_width, rank, padded, gates):
+        """Splits a fused q|latent|gate projection ([N, q_width + rank + gates] float32 or a K-split
+        stack): queries cast to `q_out`, the latent divided by its root mean square and scaled by
+        `latent_weight` into the latent pages (`padded` elements a token), sigmoid of the gate columns
+        to `gate_out` (float32).  rank 0: no latent of its own; gates 0: no gate."""
+        _dense(fused, torch.float32, "fused projection")
+        _dense(q_out, self.dtype, "q")
+        partials, stride = self._stack(fused)
+        num_slots = 0
+        if latents is not None:
+            _dense(latents, self.dtype, "latent cache")
+            num_slots = latents.shape[0] * latents.shape[1]
+        self.launches += 1
+        _check(self.core.shrike_latent_store(
+            _ptr(fused), partials, stride, _ptr(latent_weight), eps, _ptr(q_out), _ptr(latents), _ptr(slots),
+            _ptr(gate_out), self.code, fused.shape[-2], q_width, rank, padded, gates, num_slots, self._stream()),
+            "latent_store")
+
+    def head_scale(self, x, gate, heads, dim):
+        """x[n, h, :] *= gate[n, h] in place (gate float32 [N, heads])."""
+        _dense(x, self.dtype, "head outputs")
+        _dense(gate, torch.float32, "gate")
+        self.launches += 1
+        _check(self.core.shrike_head_scale(_ptr(x), _ptr(gate), self.code, x.shape[0], heads, dim, self._stream()),
+               "head_scale")
+
+    def head_linear(self, x, w, out):
+        """A product per head: out[n, h, :] = w[h] @ x[n, h, :] for x [N, H, I], w [H, O, I], out [N, H, O].
+        float32 runs this package's FFMA kernel once per head in one launch; bfloat16 is a batched library
+        product (float32 accumulation) written straight into `out`."""
+        n, heads, inner = x.shape
+        outer = w.shape[1]
+        if tuple(w.shape) != (heads, outer, inner) or tuple(out.shape) != (n, heads, outer):
+            raise KernelError(f"head_linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+        _dense(x, self.dtype, "head_linear input")
+        _dense(w, self.dtype, "head_linear weight")
+        _dense(out, self.dtype, "head_linear output")
+        if self.dtype == torch.float32:
+            self.launches += 1
+            _check(self.core.shrike_gemm_fp32_heads(_ptr(x), _ptr(w), _ptr(out), n, outer, inner, heads,
+                                                    heads * inner, inner, heads * outer, outer, self._stream()),
+                   "gemm_fp32_heads")
+            return out
+        self.library_calls += 1
+        torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+        return out
 
     def linear(self, x, w, out, bias=None, allow_partials=False):
         """x[N, K] @ w[O, K]^T (+ bias) into `out` [N, O] (float32 or the activation type).
@@ -355,10 +468,13 @@ class CudaOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None):
+                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None):
         """Attention of the batch's new tokens over the paged cache.  `max_q_len` and
         `min_q_len` are the longest and shortest entry of the batch (0: not known); `q_lens`, every
-        entry's length (host list), lets the portions kernel launch exactly the CTAs it needs."""
+        entry's length (host list), lets the portions kernel launch exactly the CTAs it needs.
+        `softcap` (a positive number) and `slopes` (float32 [num_heads]) change a score
+        s = scale * q.k, in this order: s <- softcap * tanh(s / softcap), then
+        s <- s - slopes[head] * (query position - key position)."""
         _dense(q, self.dtype, "q")
         _dense(keys, self.dtype, "key cache")
         _dense(values, self.dtype, "value cache")
@@ -373,10 +489,16 @@ class CudaOps:
             _check(lib.shrike_paged_attention_generic(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start),
                 _ptr(ctx_len), _ptr(seq_of_token), self.code, q.shape[0], num_heads, num_kv_heads,
-                page_size, num_pages, scale, window or 0, _ptr(out), self._stream()), "paged_attention")
+                page_size, num_pages, scale, window or 0, softcap or 0.0, _ptr(slopes), _ptr(out), self._stream()),
+                "paged_attention")
             return
+        modified = bool(softcap) or slopes is not None
+        if slopes is not None:
+            _dense(slopes, torch.float32, "distance slopes")
+            if slopes.numel() != num_heads:
+                raise KernelError("one distance slope per query head")
         plan = self.attention_plan(num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
-                                   q.shape[0], q_lens)
+                                   q.shape[0], q_lens, modified)
         self.launches += plan.has_single + plan.has_portions + (1 if plan.portion_splits > 1 else 0)
         has_portions = plan.has_portions
         if plan.tc_portions:
@@ -389,11 +511,11 @@ class CudaOps:
             has_portions = 0
             if not plan.has_single:
                 return
-        _check(lib.shrike_paged_attention_bf16(
+        _check(lib.shrike_paged_attention_bf16_scores(
             _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
             num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
             plan.has_single, has_portions, max_q_len, plan.splits, plan.cluster, _ptr(plan.scratch), _ptr(plan.arrivals),
-            _ptr(self.status), self._stream()),
+            _ptr(self.status), softcap or 0.0, _ptr(slopes), self._stream()),
             "paged_attention_bf16")
 
     def portion_tiles(self, q_lens, skip_single, rows) -> int:
@@ -408,7 +530,7 @@ class CudaOps:
         return tiles
 
     def attention_plan(self, num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
-                       num_tokens=0, q_lens=None):
+                       num_tokens=0, q_lens=None, modified_scores=False):
         """How a bfloat16 batch's attention is cut: which kernels run (single tokens, portions, the
         tensor-core form of the latter), the key splits and clusters of the single-token kernel, the
         key splits of the portions kernel, and their scratch.  A function of the batch's shape alone."""
@@ -432,8 +554,9 @@ class CudaOps:
                 self._arrivals = torch.zeros(max(groups, 4096), dtype=torch.int32, device=self.device)
                 self.generation += 1
             scratch, arrivals = self._scratch, self._arrivals
+        # scores with a soft cap or a distance bias go through the mma.sync kernels, which apply them
         tc_portions = bool(has_portions and self.tensor_core_attention and lib.shrike_attention_tc_available()
-                           and page_size in (8, 16, 32, 64))
+                           and page_size in (8, 16, 32, 64) and not modified_scores)
         portion_splits, portion_scratch = 1, None
         if tc_portions and num_tokens > 0:
             tiles = self.portion_tiles(q_lens, has_single, lib.shrike_attention_tc_portions_rows())
@@ -472,14 +595,21 @@ class CudaOps:
             return cluster, cluster
         return min(want // cluster * cluster, 32 * cluster), cluster
 
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}   # the codes the kernels take
+
     def silu_mul(self, gate_up, out, block=0):
-        """out = silu(gate) * up.  `block` 0: a row of gate_up is all gate columns, then all up
-        columns; b > 0: runs of b gate columns, each followed by the b up columns of the same features."""
+        """out = silu(gate) * up; see `act_mul`."""
+        self.act_mul(gate_up, out, block, "silu")
+
+    def act_mul(self, gate_up, out, block=0, activation="silu"):
+        """out = act(gate) * up, act one of `ACTIVATIONS`.  `block` 0: a row of gate_up is all gate columns,
+        then all up columns; b > 0: runs of b gate columns, each followed by the b up columns of the same features."""
         _dense(gate_up, self.dtype, "gate_up")
         _dense(out, self.dtype, "activation")
         n, inter = out.shape
         self.launches += 1
-        _check(self.core.shrike_silu_mul(_ptr(gate_up), _ptr(out), self.code, n, inter, block, self._stream()), "silu_mul")
+        _check(self.core.shrike_act_mul(_ptr(gate_up), _ptr(out), self.code, n, inter, block,
+                                        self.ACTIVATIONS[activation], self._stream()), "act_mul")
 
     @property
     def gated_rows(self) -> int:
@@ -488,8 +618,8 @@ class CudaOps:
         features.  0: keep gate rows, then up rows (no fused activation in this mode)."""
         return 16 if self.dtype == torch.bfloat16 and self.gemm_tc is not None else 0
 
-    def linear_gated(self, x, w, out) -> bool:
-        """silu(x Wg^T) * (x Wu^T) into `out` [N, I] in one kernel, for `w` [2 I, K] interleaved as
+    def linear_gated(self, x, w, out, activation="silu") -> bool:
+        """act(x Wg^T) * (x Wu^T) into `out` [N, I] in one kernel, for `w` [2 I, K] interleaved as
         `gated_rows` says.  Returns False when this shape is not served (many tokens: the caller
         then runs the product and the activation kernel, the latter with block=gated_rows)."""
         n, k = x.shape
@@ -501,8 +631,9 @@ class CudaOps:
         _dense(w, torch.bfloat16, "linear weight")
         _dense(out, torch.bfloat16, "activation")
         self.launches += 1
-        _check(self.gemm_tc.shrike_gemm_tc_gated(_ptr(x), _ptr(w), _ptr(out), n, rows, k, _ptr(self.status),
-                                                 self._stream()), "gemm_tcgen05")
+        _check(self.gemm_tc.shrike_gemm_tc_gated_act(_ptr(x), _ptr(w), _ptr(out), n, rows, k,
+                                                     self.ACTIVATIONS[activation], _ptr(self.status), self._stream()),
+               "gemm_tcgen05")
         return True
 
     def sample(self, logits, temperature, top_p, seeds, out):

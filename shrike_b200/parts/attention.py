@@ -9,6 +9,11 @@ a query at position p sees keys <= p (model_runner.py:129-150), softmax and PV i
 matrix product here (rows of Wq, Wk, Wv stacked at load), bias and rotation are
 applied to its 32-bit result and rounded once, and one kernel serves single tokens
 and portions alike.  Optional `window`: a query sees only the `window` latest keys.
+
+`SharedKeyValueAttention` is the same attention for a design whose values are its keys: one q|k
+projection, no value projection and no rotation; queries and keys normed over the whole projection,
+a query temperature that grows with the logarithm of the position, scores soft-capped and biased
+by distance, a key window.  Each of these is a parameter of its spec.
 """
 
 from __future__ import annotations
@@ -105,4 +110,77 @@ class PagedAttention:
         return ops.linear(attn, self.w_o, delta, bias=self.b_o, allow_partials=True)
 
 
+def padded_head(dim: int) -> int:
+    """The head size the attention kernels are built for: the next multiple of 16."""
+    return -(-dim // 16) * 16
+
+
+class SharedKeyValueAttention:
+    capture_safe = True   # forward() launches the same kernels for the same batch shape, whatever the positions
+
+    @staticmethod
+    def parameters(spec) -> dict[str, ParamSpec]:
+        q_out = spec.num_heads * spec.head_dim
+        k_out = spec.num_kv_heads * spec.head_dim
+        params = {
+            "q_proj.weight": ParamSpec((q_out, spec.width), "matrix"),
+            "k_proj.weight": ParamSpec((k_out, spec.width), "matrix"),
+            "o_proj.weight": ParamSpec((spec.width, q_out), "matrix"),
+        }
+        if spec.qk_norm:
+            params["q_norm.weight"] = ParamSpec((q_out,), "norm")
+            params["k_norm.weight"] = ParamSpec((k_out,), "norm")
+        return params
+
+    @staticmethod
+    def cache_needs(spec) -> list:
+        return [KVNeed(spec.num_kv_heads, padded_head(spec.head_dim), spec.window)]
+
+    def __init__(self, spec, tensors, ops, runtime):
+        self.spec, self.ops, self.runtime = spec, ops, runtime
+        self.padded = padded_head(spec.head_dim)
+        ops.check_head_dim(self.padded)
+        self.w_qk = torch.cat([tensors.pop("q_proj.weight"), tensors.pop("k_proj.weight")]).contiguous()
+        w_o = tensors.pop("o_proj.weight")
+        if self.padded != spec.head_dim:   # the kernels' heads are wider: the added columns meet zeros
+            wide = w_o.new_zeros(spec.width, spec.num_heads, self.padded)
+            wide[:, :, : spec.head_dim] = w_o.view(spec.width, spec.num_heads, spec.head_dim)
+            w_o = wide.view(spec.width, spec.num_heads * self.padded)
+        self.w_o = w_o.contiguous()
+        self.q_weight = self.k_weight = None
+        if spec.qk_norm:
+            self.q_weight = tensors.pop("q_norm.weight").to(torch.float32).contiguous()
+            self.k_weight = tensors.pop("k_norm.weight").to(torch.float32).contiguous()
+        self.slopes = None
+        if spec.slope_decay is not None:
+            slopes = [2.0 ** (-spec.slope_decay * (head + 1) / spec.num_heads) for head in range(spec.num_heads)]
+            self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(runtime.device)
+        self.qk_width = (spec.num_heads + spec.num_kv_heads) * spec.head_dim
+        self.out_width = spec.num_heads * self.padded
+
+    def forward(self, x, ctx, run):
+        spec, rt, ops = self.spec, self.runtime, self.ops
+        n = x.shape[0]
+        qk = rt.buffer("qkv", (n, self.qk_width), torch.float32)
+        qk = ops.linear(x, self.w_qk, qk, allow_partials=True)
+        group, keys, values = ctx.storage.keys_values(run.cache)
+        view = ctx.groups[group]
+        q = rt.buffer("q", (n, self.out_width), rt.act_dtype)
+        ops.qk_norm_store(
+            qk, self.q_weight, self.k_weight, spec.eps, ctx.positions, spec.q_temperature, q,
+            keys if run.writes_cache else None, values if run.writes_cache else None, view.slot_mapping,
+            spec.num_heads, spec.num_kv_heads, spec.head_dim, self.padded,
+        )
+        attn = rt.buffer("attn_out", (n, self.out_width), rt.act_dtype)
+        ops.paged_attention(
+            q, keys, values, view.block_table, ctx.q_start, ctx.ctx_len, ctx.seq_of_token,
+            spec.num_heads, spec.num_kv_heads, self.padded, spec.scale, spec.window, attn,
+            max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, min_q_len=ctx.min_q_len, q_lens=ctx.q_lens,
+            softcap=spec.softcap, slopes=self.slopes,
+        )
+        delta = rt.buffer("mixer_delta", (n, spec.width), torch.float32)
+        return ops.linear(attn, self.w_o, delta, allow_partials=True)
+
+
 register_part("mixer", "attention", PagedAttention)
+register_part("mixer", "shared_kv_attention", SharedKeyValueAttention)

@@ -66,11 +66,13 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values in pages: `window` None keeps all, else the last `window`."""
+    """Keys and values in pages: `window` None keeps all, else the last `window`.  `planes` 2: a key
+    and a value tensor; 1: one tensor a token (a latent that serves as both), at half the memory."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)

@@ -1,4 +1,10 @@
-"""Pre-norm residual block: x += mixer(norm(x)); x += ffn(norm(x))
+"""Residual blocks.
+
+`BranchNormBlock`: the norm sits on a branch's OUTPUT, x += norm(mixer(x)); x += norm(ffn(x)), and both
+branches read x itself; the feed-forward may be absent.  The residual sum is 32-bit; a 16-bit engine
+gets the rounded residual a branch reads from the kernel that made the sum.
+
+`PreNormBlock`: pre-norm residual block: x += mixer(norm(x)); x += ffn(norm(x))
 (shrike/models/qwen.py:147-150).  The residual `resid` is float32; a branch output
 is handed on as `delta` and added by the next norm kernel.
 
@@ -49,4 +55,29 @@ class PreNormBlock:
         return resid, delta
 
 
+class BranchNormBlock:
+    capture_safe = True
+
+    def __init__(self, mixer, mixer_norm, feed_forward=None, feed_forward_norm=None):
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self.mixer = mixer
+        self.mixer_norm = mixer_norm
+        self.feed_forward = feed_forward
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(self, resid, delta, ctx, run):
+        if delta is not None:
+            raise NotImplementedError("a branch-norm block takes a residual with nothing pending")
+        # the block before (if of this kind) left the residual in the activation type with its last sum
+        held = ctx.carried.pop("residual_cast", None)
+        hidden = held[1] if held is not None and held[0] is resid else self.mixer_norm.norm_add(resid, None)
+        hidden = self.mixer_norm.norm_add(resid, self.mixer.forward(hidden, ctx, run))
+        if self.feed_forward is not None:
+            hidden = self.feed_forward_norm.norm_add(resid, self.feed_forward.forward(hidden, ctx))
+        ctx.carried["residual_cast"] = (resid, hidden)
+        return resid, None
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "branch_norm", BranchNormBlock)

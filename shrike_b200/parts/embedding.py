@@ -33,6 +33,28 @@ class TokenEmbedding:
         return resid
 
 
+class TokenPositionEmbedding:
+    """Token row plus the learned vector of the token's position, summed in 32-bit."""
+
+    capture_safe = True
+
+    @staticmethod
+    def parameters(spec) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((spec.vocab, spec.width), "table"),
+                "positions": ParamSpec((spec.max_positions, spec.width), "table")}
+
+    def __init__(self, spec, tensors, ops, runtime):
+        self.spec, self.ops, self.runtime = spec, ops, runtime
+        self.table = tensors["weight"]
+        self.position_table = tensors["positions"].to(self.table.dtype).contiguous()
+
+    def forward(self, ctx) -> torch.Tensor:
+        resid = self.runtime.buffer("resid", (ctx.num_tokens, self.spec.width), torch.float32)
+        self.ops.embed(ctx.token_ids, self.table, resid, ctx.previous_tokens,
+                       position_table=self.position_table, positions=ctx.positions)
+        return resid
+
+
 class LMHead:
     capture_safe = True
 
@@ -52,4 +74,5 @@ class LMHead:
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "token_position_embedding", TokenPositionEmbedding)
 register_part("head", "lm_head", LMHead)

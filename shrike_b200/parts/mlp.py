@@ -11,6 +11,9 @@ import torch
 from .base import ParamSpec, register_part
 
 
+ACTIVATIONS = ("silu", "gelu_tanh")   # gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+
+
 class GatedMLP:
     capture_safe = True   # forward() launches the same kernels for the same batch shape, whatever the positions
 
@@ -23,8 +26,9 @@ class GatedMLP:
         }
 
     def __init__(self, spec, tensors, ops, runtime):
-        if spec.activation != "silu":
-            raise ValueError(f"gated feed-forward activation {spec.activation!r} has no kernel; known: silu")
+        if spec.activation not in ACTIVATIONS:
+            raise ValueError(f"gated feed-forward activation {spec.activation!r} has no kernel; known: "
+                             + ", ".join(ACTIVATIONS))
         self.spec = spec
         self.ops = ops
         self.runtime = runtime
@@ -43,13 +47,10 @@ class GatedMLP:
         spec, rt, ops = self.spec, self.runtime, self.ops
         n = x.shape[0]
         act = rt.buffer("ffn_act", (n, spec.intermediate), rt.act_dtype)
-        if not (self.run and ops.linear_gated(x, self.w_gate_up, act)):
+        if not (self.run and ops.linear_gated(x, self.w_gate_up, act, spec.activation)):
             gate_up = rt.buffer("gate_up", (n, 2 * spec.intermediate), rt.act_dtype)
             ops.linear(x, self.w_gate_up, gate_up)
-            if self.run:
-                ops.silu_mul(gate_up, act, block=self.run)
-            else:
-                ops.silu_mul(gate_up, act)
+            ops.act_mul(gate_up, act, self.run, spec.activation)
         delta = rt.buffer("ffn_delta", (n, spec.width), torch.float32)
         return ops.linear(act, self.w_down, delta, allow_partials=True)
 

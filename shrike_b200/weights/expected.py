@@ -23,12 +23,11 @@ def expected_tensors(config: ModelConfig) -> dict[str, ParamSpec]:
         table[names.embedding_name(local)] = param
     for index, layer in enumerate(config.layers):
         for role, category, spec in layer.roles():
-            prefix = names.layer_part(index, role)
             for local, param in part_class(category, spec.kind).parameters(spec).items():
-                table[prefix + local] = param
+                table[names.layer_tensor(index, role, local)] = param
     norm = config.final_norm
     for local, param in part_class("norm", norm.kind).parameters(norm).items():
-        table[names.final_norm_prefix + local] = param
+        table[names.final_norm_name(local)] = param
     for local, param in part_class("head", config.head.kind).parameters(config.head).items():
         table[names.head_name(local)] = param
     return table

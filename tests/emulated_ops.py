@@ -25,11 +25,78 @@ class EmulatedOps:
         if head_dim % 16 or not 16 <= head_dim <= 256:
             raise ValueError(f"head size {head_dim} is not served")
 
-    def embed(self, ids, table, out, previous=None):
+    def embed(self, ids, table, out, previous=None, position_table=None, positions=None):
         ids = ids.long()
         if previous is not None and (ids < 0).any():
             ids = torch.where(ids < 0, previous.long()[(-1 - ids).clamp(min=0, max=previous.numel() - 1)], ids)
         out.copy_(table[ids].float())
+        if position_table is not None:
+            out.add_(position_table[positions.long()].float())
+
+    @staticmethod
+    def _norm(x, weight, bias, eps, layer_norm):
+        if layer_norm:
+            x = x - x.mean(-1, keepdim=True)
+        y = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight
+        return y if bias is None else y + bias
+
+    def norm_add(self, resid, branch, weight, bias, eps, out, layer_norm=True):
+        if branch is not None:
+            summed = branch.float().sum(0) if branch.dim() == 3 else branch.float()
+            resid.add_(self._norm(summed, weight, bias, eps, layer_norm))
+        if out is not None:
+            out.copy_(resid.to(out.dtype))
+
+    def gather_norm(self, resid, rows, weight, bias, eps, out, layer_norm=True):
+        out.copy_(self._norm(resid[rows.long()], weight, bias, eps, layer_norm).to(out.dtype))
+
+    def qk_norm_store(self, qk, q_weight, k_weight, eps, positions, temperature, q_out, keys, values, slots,
+                      num_heads, num_kv_heads, dim, padded):
+        if qk.dim() == 3:
+            qk = qk.sum(0)
+        n = qk.shape[0]
+        q, k = qk[:, : num_heads * dim].float(), qk[:, num_heads * dim:].float()
+        v = k
+        if q_weight is not None:
+            q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+        if k_weight is not None:
+            k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        if temperature is not None:
+            coef, every = temperature
+            steps = torch.div(positions.long() + 1, every, rounding_mode="floor") + 1
+            q = q * (1.0 + coef * torch.log(steps.float()))[:, None]
+
+        def pad(t, heads):
+            wide = torch.zeros(n, heads, padded)
+            wide[:, :, :dim] = t.view(n, heads, dim)
+            return wide
+
+        q_out.copy_(pad(q, num_heads).view(n, -1).to(q_out.dtype))
+        if keys is not None:
+            self.kv_write(pad(k, num_kv_heads).view(n, -1), pad(v, num_kv_heads).view(n, -1), keys, values, slots)
+
+    def latent_store(self, fused, latent_weight, eps, q_out, latents, slots, gate_out, q_width, rank, padded, gates):
+        if fused.dim() == 3:
+            fused = fused.sum(0)
+        n = fused.shape[0]
+        q_out.copy_(fused[:, :q_width].to(q_out.dtype))
+        if gates:
+            gate_out.copy_(torch.sigmoid(fused[:, q_width + rank:].float()))
+        if rank and latents is not None:
+            c = fused[:, q_width: q_width + rank].float()
+            c = c / torch.sqrt(c.pow(2).mean(-1, keepdim=True) + eps) * latent_weight
+            wide = torch.zeros(n, padded)
+            wide[:, :rank] = c
+            flat = latents.view(-1, latents.shape[-2] * latents.shape[-1])
+            flat[slots.long()] = wide.to(flat.dtype)
+
+    def head_scale(self, x, gate, heads, dim):
+        n = x.shape[0]
+        x.copy_((x.float().view(n, heads, dim) * gate[:, :, None]).view(n, -1).to(x.dtype))
+
+    def head_linear(self, x, w, out):
+        out.copy_(torch.einsum("nhi,hoi->nho", x.float(), w.float()).to(out.dtype))
+        return out
 
     def add_rmsnorm(self, resid, delta, weight, eps, out):
         if delta is not None:
@@ -93,7 +160,7 @@ class EmulatedOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None):
+                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None):
         page = keys.shape[1]
         group = num_heads // num_kv_heads
         n = q.shape[0]
@@ -110,15 +177,27 @@ class EmulatedOps:
             v = values[pages, idx % page].float()
             qt = q[token].float().view(num_kv_heads, group, head_dim)
             scores = torch.einsum("kgd,ckd->kgc", qt, k) * scale
+            if softcap:
+                scores = softcap * torch.tanh(scores / softcap)
+            if slopes is not None:
+                scores = scores - slopes.view(num_kv_heads, group, 1) * (last - idx).float()
             probs = scores.softmax(-1)
             o = torch.einsum("kgc,ckd->kgd", probs, v)
             out[token] = o.reshape(-1).to(out.dtype)
 
     def silu_mul(self, gate_up, out):
+        self.act_mul(gate_up, out)
+
+    def act_mul(self, gate_up, out, block=0, activation="silu"):
+        assert block == 0
         inter = out.shape[1]
         g = gate_up[:, :inter].float()
         u = gate_up[:, inter:].float()
-        out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
+        if activation == "gelu_tanh":
+            act = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+        else:
+            act = g * torch.sigmoid(g)
+        out.copy_((act * u).to(out.dtype))
 
     def sample(self, logits, temperature, top_p, seeds, out):
         for row in range(logits.shape[0]):
