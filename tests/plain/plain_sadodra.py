@@ -66,6 +66,42 @@ def distance_slopes(heads: int, dtype) -> torch.Tensor:
     return torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=dtype)
 
 
+def attend(q, k, v, scale, window=None, softcap=None, slopes=None, first_position=0) -> torch.Tensor:
+    """Softmax attention of queries q [m, H, D] at positions first_position .. over keys k [n, G, D]
+    and values v [n, G, Dv] at positions 0 .. n - 1 (n = first_position + m): head h uses key/value
+    head h // (H / G); score = scale q.k, soft-capped, less slope_h * distance; query i sees key j
+    with 0 <= i - j (< window)."""
+    m, H, _ = q.shape
+    n, G = k.shape[0], k.shape[1]
+    i = torch.arange(first_position, first_position + m)[:, None]
+    j = torch.arange(n)[None, :]
+    seen = j <= i
+    if window is not None:
+        seen = seen & (i - j < window)
+    out = torch.empty(m, H, v.shape[-1], dtype=q.dtype)
+    for head in range(H):
+        s = (q[:, head] @ k[:, head // (H // G)].T) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        if slopes is not None:
+            s = s - slopes[head] * (i - j).to(q.dtype)
+        s = s.masked_fill(~seen, float("-inf"))
+        out[:, head] = s.softmax(-1) @ v[:, head // (H // G)]
+    return out
+
+
+def normed_queries_keys(q, k, q_weight, k_weight, eps, temperature, positions):
+    """q and k [n, all heads * D], each divided by its root mean square over the whole row and scaled;
+    the query then times its temperature at its position."""
+    q = rms_unit(q, eps) * q_weight
+    k = rms_unit(k, eps) * k_weight
+    if temperature is not None:
+        coef, every = temperature
+        steps = torch.div(positions + 1, every, rounding_mode="floor") + 1
+        q = q * (1.0 + coef * torch.log(steps.to(q.dtype)))[:, None]
+    return q, k
+
+
 def windowed_attention(h, weights, prefix, mixer, eps, rounding) -> torch.Tensor:
     """The `attention` mixer on a whole sequence h [n, W] -> [n, W]."""
     n, dtype = h.shape[0], h.dtype
@@ -73,27 +109,13 @@ def windowed_attention(h, weights, prefix, mixer, eps, rounding) -> torch.Tensor
     q = _r(h @ weights[prefix + "q"].to(dtype).T, rounding)
     k = _r(h @ weights[prefix + "k"].to(dtype).T, rounding)
     v = k.view(n, G, D)                                    # the values are the keys as projected
-    q = rms_unit(q, eps) * weights[prefix + "q.norm"].to(dtype)
-    k = rms_unit(k, eps) * weights[prefix + "k.norm"].to(dtype)
     temp = mixer.get("q_temp")
-    if temp is not None:
-        q = q * query_temperature(n, temp["coef"], temp["every"], dtype)[:, None]
+    q, k = normed_queries_keys(q, k, weights[prefix + "q.norm"].to(dtype), weights[prefix + "k.norm"].to(dtype), eps,
+                               None if temp is None else (temp["coef"], temp["every"]), torch.arange(n))
     q, k = _r(q, rounding).view(n, H, D), _r(k, rounding).view(n, G, D)
-    group = H // G
-    i, j = torch.arange(n)[:, None], torch.arange(n)[None, :]
-    seen = (j <= i)
-    if mixer.get("mask") is not None:
-        seen = seen & (i - j < mixer["mask"]["size"])
-    slopes = distance_slopes(H, dtype)
-    out = torch.empty(n, H, D, dtype=dtype)
-    for head in range(H):
-        s = (q[:, head] @ k[:, head // group].T) * mixer["scale"]
-        cap = mixer.get("softcap")
-        if cap:
-            s = cap * torch.tanh(s / cap)
-        s = s - slopes[head] * (i - j).to(dtype)
-        s = s.masked_fill(~seen, float("-inf"))
-        out[:, head] = s.softmax(-1) @ v[:, head // group]
+    mask = mixer.get("mask")
+    out = attend(q, k, v, mixer["scale"], None if mask is None else mask["size"], mixer.get("softcap"),
+                 distance_slopes(H, dtype))
     out = _r(out.reshape(n, H * D), rounding)
     return out @ weights[prefix + "o"].to(dtype).T
 
@@ -113,12 +135,7 @@ def latent_attention(h, c, weights, prefix, mixer, rounding) -> torch.Tensor:
     k = _r(c @ weights[prefix + "uk"].to(dtype).T, rounding).view(n, H, D)
     v = _r(c @ weights[prefix + "uv"].to(dtype).T, rounding).view(n, H, V)
     gate = torch.sigmoid(h @ weights[prefix + "g"].to(dtype).T)          # [n, H]
-    i, j = torch.arange(n)[:, None], torch.arange(n)[None, :]
-    out = torch.empty(n, H, V, dtype=dtype)
-    for head in range(H):
-        s = (q[:, head] @ k[:, head].T) * mixer["scale"]
-        s = s.masked_fill(j > i, float("-inf"))
-        out[:, head] = (s.softmax(-1) @ v[:, head]) * gate[:, head, None]
+    out = attend(q, k, v, mixer["scale"]) * gate[:, :, None]
     out = _r(out.reshape(n, H * V), rounding)
     return out @ weights[prefix + "o"].to(dtype).T
 
@@ -159,3 +176,15 @@ def forward(raw: dict, weights: dict, tokens, dtype=torch.float64, rounding: boo
     x = _r(layer_norm(x, weights["final.norm"].to(dtype), weights["final.norm.b"].to(dtype), eps), rounding)
     logits = x @ weights["head"].to(dtype).T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def greedy_continue(raw: dict, weights: dict, prompt, count: int, dtype=torch.float64):
+    """`count` greedy tokens after `prompt`, each from a whole-sequence pass, and the gap between
+    the two largest logits at each step."""
+    tokens, margins = list(prompt), []
+    for _ in range(count):
+        logits = forward(raw, weights, tokens, dtype=dtype)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        tokens.append(int(torch.argmax(logits)))
+    return tokens[len(prompt):], margins
