@@ -76,16 +76,16 @@ def sharpened(tensors: dict) -> dict:
     """Random weights leave every attention nearly uniform, which hides a key that is wrongly seen or
     missed.  This scales what sets the size of the scores (the query norm's weight, the latent's key
     projection, the query projection of latent layers) so that a softmax row has a few large
-    entries, and gives the position vectors and the norm biases a size that matters."""
+    entries (scores a few units apart: more would make the logits hang on single roundings), and gives the position vectors and the norm biases a size that matters."""
     out = {}
     for name, tensor in tensors.items():
         t = tensor.clone()
         if name.endswith(".mix.q.norm"):
-            t *= 3.0
+            t *= 1.5
         elif name.endswith(".mix.uk"):
-            t *= 25.0
+            t *= 8.0
         elif name.endswith(".mix.q") and name.replace(".mix.q", ".mix.uk") in tensors:
-            t *= 10.0
+            t *= 4.0
         elif name == "pos":
             t *= 2.0
         out[name] = t
