@@ -680,6 +680,141 @@ def run_timeline(args) -> dict:
             "step_us": round(step[-1].time_range.end - step[0].time_range.start, 1)}
 
 
+def run_design(args) -> dict:
+    """The Sadodra decoder beside the Qwen2 decoder of the same widths, layer count and vocabulary (the
+    closest model this engine serves), random weights: one 2,048-token prompt in one step, and decoding
+    at --batch sequences of --context tokens, device-timed through the step function and the sampling
+    kernel; for each, the kernels of one step by the time they take (CUPTI activity records).
+    `--design 1.5b` or `7b` picks the pair of shape files; `--layers` cuts both models alike."""
+    import numpy as np
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    import shrike_b200.models  # noqa: F401
+    from shrike_b200.config import parse_config
+    from shrike_b200.engine.batch import StepEntry
+    from shrike_b200.engine.llm_engine import LLMEngine
+    from shrike_b200.shapes import shape_config
+    from shrike_b200.weights.random_init import random_tensors
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda:0")
+    context, batch = args.context, args.batch
+    peaks = load_peaks()
+
+    def kernels_of(run_step) -> list:
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            run_step()
+            torch.cuda.synchronize()
+        totals: dict = {}
+        for event in prof.events():
+            if event.device_type == torch.autograd.DeviceType.CUDA and "Memcpy" not in event.name and "Memset" not in event.name:
+                name = event.name.split("(")[0].split("<")[0].split("::")[-1]
+                held = totals.setdefault(name, [0.0, 0])
+                held[0] += event.time_range.end - event.time_range.start
+                held[1] += 1
+        return [{"kernel": name, "us": round(us, 1), "launches": count}
+                for name, (us, count) in sorted(totals.items(), key=lambda item: -item[1][0])][:12]
+
+    def measure(name: str, raw: dict) -> dict:
+        config = parse_config(raw)
+        tensors = random_tensors(config, seed=0, device=device, dtype=torch.bfloat16)
+        pages = batch * (-(-(context + args.steps + args.warmup + 16) // BLOCK_SIZE)) + -(-PREFILL_TOKENS // BLOCK_SIZE) + 64
+        engine = LLMEngine(None, block_size=BLOCK_SIZE, num_blocks=pages, max_tokens_per_step=4096, max_running=64,
+                           dtype="bfloat16", config=config, tensors=tensors)
+        del tensors
+        runner = engine.runner
+        rng = np.random.default_rng(0)
+        vocab = config.vocab_size
+
+        def prefill_once():
+            cache = runner.cache.open()
+            ids = rng.integers(0, vocab, PREFILL_TOKENS).tolist()
+            runner.cache.append(cache, 0, PREFILL_TOKENS)
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step([StepEntry(cache, ids, 0, [PREFILL_TOKENS - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            runner.cache.free(cache)
+            return start.elapsed_time(stop)
+
+        runner.use_graphs = False
+        prefill_ms = statistics.median([prefill_once() for _ in range(args.warmup + 5)][args.warmup:])
+        prefill_kernels = kernels_of(prefill_once)
+        runner.use_graphs = True
+
+        caches = []
+        for _ in range(batch):
+            cache = runner.cache.open()
+            ids = rng.integers(0, vocab, context - 1).tolist()
+            runner.cache.append(cache, 0, len(ids))
+            runner.step([StepEntry(cache, ids, 0, [])])
+            caches.append(cache)
+        fed = [context - 1]
+
+        def decode_step():
+            entries = []
+            for index, cache in enumerate(caches):
+                runner.cache.append(cache, fed[0], 1)
+                entries.append(StepEntry(cache, [-1 - index] if fed[0] >= context else [5], fed[0], [0], (0.0, 1.0, 0)))
+            fed[0] += 1
+            return runner.step(entries, sample=True)[1]
+
+        for _ in range(args.warmup):
+            decode_step()
+        torch.cuda.synchronize()
+        launches = engine.ops.launches
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            drawn = decode_step()
+        stop.record()
+        drawn.tolist()
+        torch.cuda.synchronize()
+        decode_ms = start.elapsed_time(stop) / args.steps
+        launches = (engine.ops.launches - launches) // args.steps
+        runner.use_graphs = False   # kernel by kernel, so that the records name every kernel of the step
+        decode_step()
+        decode_kernels = kernels_of(decode_step)
+        weight_bytes = engine.runner.model.weight_bytes()
+        cache_bytes = runner.bytes_per_page / BLOCK_SIZE
+        result = {
+            "model": name, "layers": config.num_layers, "weights_GB": round(weight_bytes / 1e9, 2),
+            "cache_bytes_per_token": int(cache_bytes),
+            "prefill": {"tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3), "tok_s": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1),
+                        "kernels": prefill_kernels},
+            "decode": {"batch": batch, "context": context, "ms_per_step": round(decode_ms, 4),
+                       "tok_s": round(batch * 1000.0 / decode_ms, 1), "launches_per_step": launches,
+                       "GBps_weights_and_cache": round((weight_bytes + batch * context * cache_bytes) / decode_ms / 1e6, 1),
+                       "kernels": decode_kernels},
+        }
+        for cache in caches:
+            runner.cache.free(cache)
+        del engine, runner
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        return result
+
+    ours = dict(shape_config(f"sadodra-{args.design}"))
+    theirs = dict(shape_config(f"qwen2.5-{args.design}"))
+    if args.layers:
+        ours["layers"] = ours["layers"][: args.layers]
+        theirs["num_hidden_layers"] = args.layers
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.perf_counter()
+    results = [measure(f"Sadodra at Qwen2.5-{args.design.upper()} widths", ours),
+               measure(f"Qwen2.5-{args.design.upper()} shape", theirs)]
+    sampler.stop()
+    return {"case": "design", "design": "Sadodra", "closest": "Qwen2ForCausalLM", "dtype": "bf16",
+            "data": "synthetic: seeded random weights and uniform random token ids", "peaks": peaks,
+            "models": results, "clocks": sampler.summary([(t0, time.perf_counter())])}
+
+
 def run_reference(args) -> dict:
     reference = ROOT / "baseline" / "_ref"
     if not (reference / "shrike").is_dir():
@@ -707,10 +842,13 @@ def main():
     parser.add_argument("--skip-mixed", action="store_true", help="leave the mixed workload out of the default line")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                         help="prompt length of --case attention_portions")
+    parser.add_argument("--design", default="1.5b", choices=["1.5b", "7b"],
+                        help="--case design: the widths at which the Sadodra decoder and the Qwen2 decoder are compared")
     parser.add_argument("--case", default=None,
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
                              "gemm_qkv, attention_single, attention_portions; --batch gives tokens / sequences.  timeline: per-kernel "
-                             "times inside one captured decode step (--layers, default 6)")
+                             "times inside one captured decode step (--layers, default 6).  design: the Sadodra decoder "
+                             "beside the Qwen2 decoder of equal widths (--design), prefill and decode")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this engine runs on a single B200 (asked for {args.gpus})")
@@ -718,6 +856,9 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.case == "timeline":
         print(json.dumps(run_timeline(args)))
+        return
+    if args.case == "design":
+        print(json.dumps(run_design(args)))
         return
     if args.case:
         print(json.dumps(run_case(args)))
