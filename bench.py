@@ -706,15 +706,20 @@ def run_design(args) -> dict:
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             run_step()
             torch.cuda.synchronize()
+        events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+                         and "Memcpy" not in e.name and "Memset" not in e.name), key=lambda e: e.time_range.start)
+        # kernels overlap (each may start while the one before it runs), so a kernel is charged the time
+        # from the end of the kernel before it to its own end: what the step would save without it
         totals: dict = {}
-        for event in prof.events():
-            if event.device_type == torch.autograd.DeviceType.CUDA and "Memcpy" not in event.name and "Memset" not in event.name:
-                name = event.name.split("(")[0].split("<")[0].split("::")[-1]
-                held = totals.setdefault(name, [0.0, 0])
-                held[0] += event.time_range.end - event.time_range.start
-                held[1] += 1
+        previous_end = events[0].time_range.start if events else 0
+        for event in events:
+            name = event.name.split("(")[0].split("<")[0].split("::")[-1].replace("void ", "")
+            held = totals.setdefault(name, [0.0, 0])
+            held[0] += max(0.0, event.time_range.end - max(previous_end, 0))
+            held[1] += 1
+            previous_end = max(previous_end, event.time_range.end)
         return [{"kernel": name, "us": round(us, 1), "launches": count}
-                for name, (us, count) in sorted(totals.items(), key=lambda item: -item[1][0])][:12]
+                for name, (us, count) in sorted(totals.items(), key=lambda item: -item[1][0])][:14]
 
     def measure(name: str, raw: dict) -> dict:
         config = parse_config(raw)

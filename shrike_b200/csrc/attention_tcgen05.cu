@@ -117,6 +117,10 @@ struct Args {
   int num_tokens;
   int num_seqs;
   const int* seq_of_token;   // [tokens], for the combine
+  // optional changes to a score s = scale * q.k, in this order (both off: softcap 0, slopes null):
+  // s <- softcap * tanh(s / softcap); s <- s - slopes[head] * (query position - key position)
+  float scale, softcap;
+  const float* slopes;
 };
 
 // Which (sequence, query tile) a CTA with work index `work` owns: sequences in order, each with its
@@ -419,6 +423,9 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const unsigned lane_base = static_cast<unsigned>(quarter * 32) << 16;
     const unsigned tmem_chain = sh->tmem_base + chain * CHAIN_COLS + lane_base, tmem_o = tmem_chain + O_COL;
     float row_max = -INFINITY, row_sum = 0.f;
+    const bool modified = args.softcap > 0.f || args.slopes != nullptr;
+    const float slope = args.slopes != nullptr ? args.slopes[head] : 0.f;
+    const float scale_log2 = modified ? 1.0f : args.scale_log2;
     bool ok = true;
     for (int h = 0; h < my_steps && ok; ++h) {
       ok = mbar_wait(&sh->s_full[chain], h & 1, &sh->abort, args.status, ERR_SOFTMAX);
@@ -432,6 +439,22 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       fence_before_sync();
       mbar_arrive(&sh->s_read[chain]);    // the scores are in registers: their columns may take the next step
       const int key_base = tile_lo * KEYS + h * HALF_KEYS;
+      if (modified) {
+        // the scores leave here as the softmax takes them (times log2 e): the scale below is then 1.
+        // tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1) with the hardware exponential and reciprocal
+        // (absolute error about 1e-7, far below what bfloat16 queries and keys leave in a score)
+        const float cap_in = args.softcap > 0.f ? 2.0f * LOG2E * args.scale / args.softcap : 0.f;
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float sc = __uint_as_float(v[g][j]);
+            if (args.softcap > 0.f) sc = args.softcap * (1.0f - __fdividef(2.0f, fast_exp2(sc * cap_in) + 1.0f));
+            else sc *= args.scale;
+            sc = (sc - slope * static_cast<float>(last - (key_base + g * 32 + j))) * LOG2E;
+            v[g][j] = __float_as_uint(sc);
+          }
+      }
       if (key_base < first || key_base + HALF_KEYS - 1 > last) {   // only steps at the edge of the row's range pay for masking
 #pragma unroll
         for (int g = 0; g < 2; ++g)
@@ -449,7 +472,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
           for (int a = 0; a < 4; ++a) part_max[a] = max3(part_max[a], __uint_as_float(v[g][j + 2 * a]), __uint_as_float(v[g][j + 2 * a + 1]));
       float step_max = fmaxf(max3(part_max[0], part_max[1], part_max[2]), part_max[3]);
-      step_max *= args.scale_log2;
+      step_max *= scale_log2;
       // The base of the exponentials follows the running maximum lazily: it moves (and O is
       // rescaled) only when the maximum has grown by more than 2^8; until then probabilities
       // are at most 2^8, which float32 sums and bfloat16 products hold without loss.
@@ -462,7 +485,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         row_max = new_max;
       }
       const float base = row_max == -INFINITY ? 0.f : row_max;
-      const unsigned long long scale_pair = pair_of(args.scale_log2, args.scale_log2), base_pair = pair_of(-base, -base);
+      const unsigned long long scale_pair = pair_of(scale_log2, scale_log2), base_pair = pair_of(-base, -base);
       unsigned long long sum_pair[2] = {pair_of(0.f, 0.f), pair_of(0.f, 0.f)};
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
@@ -652,13 +675,16 @@ SHRIKE_API long long shrike_attention_tc_portions_scratch_floats(int num_tokens,
 // Portions (q_len > 1) of a batch; entries with q_len == 1 are skipped when skip_single.
 // q [tokens, heads * D] and out alike; caches [pages, page_size, kv heads, D]; page_size one of
 // 8, 16, 32, 64.
-SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_cache, const void* v_cache,
-                                                  const int* block_table, int max_blocks, const int* q_start,
-                                                  const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
-                                                  int num_kv_heads, int page_size, int num_pages, float scale,
-                                                  int window, void* out, int skip_single, int max_q_len, int* status,
-                                                  int splits, float* scratch, int portion_tiles, const int* seq_of_token,
-                                                  cudaStream_t stream) {
+// `softcap` > 0 and `slopes` (float32 [num_heads], or null) change a score s = scale * q.k to
+// softcap * tanh(s / softcap) and then to s - slopes[head] * (query position - key position).
+SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void* q, const void* k_cache, const void* v_cache,
+                                                         const int* block_table, int max_blocks, const int* q_start,
+                                                         const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
+                                                         int num_kv_heads, int page_size, int num_pages, float scale,
+                                                         int window, void* out, int skip_single, int max_q_len, int* status,
+                                                         int splits, float* scratch, int portion_tiles,
+                                                         const int* seq_of_token, float softcap, const float* slopes,
+                                                         cudaStream_t stream) {
   using namespace tcattn;
   if (num_seqs <= 0 || num_tokens <= 0) return SHRIKE_OK;
   if (splits < 1 || splits > 32 || (splits > 1 && (scratch == nullptr || seq_of_token == nullptr))) return SHRIKE_BAD_ARGUMENT;
@@ -698,6 +724,9 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
   args.window = window;
   args.skip_single = skip_single;
   args.scale_log2 = scale * LOG2E;
+  args.scale = scale;
+  args.softcap = softcap > 0.f ? softcap : 0.f;
+  args.slopes = slopes;
   args.splits = splits;
   args.num_tokens = num_tokens;
   args.num_seqs = num_seqs;
@@ -714,6 +743,19 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_c
   return shrike_launch_status();
 }
 
+SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_cache, const void* v_cache,
+                                                  const int* block_table, int max_blocks, const int* q_start,
+                                                  const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
+                                                  int num_kv_heads, int page_size, int num_pages, float scale,
+                                                  int window, void* out, int skip_single, int max_q_len, int* status,
+                                                  int splits, float* scratch, int portion_tiles, const int* seq_of_token,
+                                                  cudaStream_t stream) {
+  return shrike_paged_attention_tc_portions_scores(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, num_tokens,
+                                                   num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window, out,
+                                                   skip_single, max_q_len, status, splits, scratch, portion_tiles, seq_of_token,
+                                                   0.f, nullptr, stream);
+}
+
 #else  // other head sizes: the mma.sync kernel serves them
 
 SHRIKE_API int shrike_attention_tc_available() { return 0; }
@@ -723,6 +765,11 @@ SHRIKE_API long long shrike_attention_tc_portions_scratch_floats(int, int, int) 
 SHRIKE_API int shrike_paged_attention_tc_portions(const void*, const void*, const void*, const int*, int, const int*,
                                                   const int*, int, int, int, int, int, int, float, int, void*, int, int,
                                                   int*, int, float*, int, const int*, cudaStream_t) {
+  return SHRIKE_BAD_ARGUMENT;
+}
+SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void*, const void*, const void*, const int*, int, const int*,
+                                                         const int*, int, int, int, int, int, int, float, int, void*, int, int,
+                                                         int*, int, float*, int, const int*, float, const float*, cudaStream_t) {
   return SHRIKE_BAD_ARGUMENT;
 }
 

@@ -19,6 +19,21 @@ namespace branch {
 
 constexpr int MAX_PER_THREAD = 8;
 
+template <typename T> __device__ __forceinline__ void load_sum4(const T* base, long long stride, int partials, float (&v)[4]);
+template <> __device__ __forceinline__ void load_sum4<float>(const float* base, long long stride, int partials, float (&v)[4]) {
+  sum_partials4(base, stride, partials, v);
+}
+template <> __device__ __forceinline__ void load_sum4<__nv_bfloat16>(const __nv_bfloat16* base, long long stride, int partials,
+                                                                     float (&v)[4]) {
+  load4<__nv_bfloat16>(base, v);
+  for (int p = 1; p < partials; ++p) {
+    float more[4];
+    load4<__nv_bfloat16>(base + p * stride, more);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = __fadd_rn(v[e], more[e]);
+  }
+}
+
 template <typename T> __device__ __forceinline__ float load_sum(const T* base, long long stride, int partials);
 template <> __device__ __forceinline__ float load_sum<float>(const float* base, long long stride, int partials) {
   return sum_partials(base, stride, partials);
@@ -29,14 +44,14 @@ template <> __device__ __forceinline__ float load_sum<__nv_bfloat16>(const __nv_
   return sum;
 }
 
-// One block per row; a thread holds elements threadIdx.x + i * blockDim.x in registers between the
-// statistics and the scaling, so a row is read once.
+// One block per row; a thread holds its groups of VEC elements (group threadIdx.x + i * blockDim.x) in
+// registers between the statistics and the scaling, so a row is read once; VEC = 4 uses 16-byte accesses.
 //   rows == nullptr: y = norm(sum of the branch's partials); resid[row] += y; out[row] = resid[row]
 //                    (out may be null).  branch == nullptr: out[row] = resid[row] only.
 //   rows != nullptr: out[r] = norm(resid[rows[r]]); nothing else is written.
 // norm(v) = (v - mean) / sqrt(var + eps) * w + b with var the mean squared deviation (layer_norm), or
 // v / sqrt(mean(v^2) + eps) * w (+ b).
-template <typename TD, typename TO>
+template <typename TD, typename TO, int VEC>
 __global__ void __launch_bounds__(1024, 1)
 norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int partials, long long partial_stride,
                  const int* __restrict__ rows, const float* __restrict__ weight, const float* __restrict__ bias,
@@ -48,21 +63,43 @@ norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int p
   const int row = rows != nullptr ? rows[out_row] : out_row;
   float* x = resid + static_cast<size_t>(row) * width;
   TO* y = out != nullptr ? out + static_cast<size_t>(out_row) * width : nullptr;
+  const int groups = width / VEC;
   if (rows == nullptr && branch == nullptr) {
     if (y != nullptr)
-      for (int i = threadIdx.x; i < width; i += blockDim.x) y[i] = from_float<TO>(x[i]);
+      for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        if (VEC == 4) {
+          float v[4];
+          load4<float>(x + g * 4, v);
+          store4<TO>(y + g * 4, v);
+        } else {
+          y[g] = from_float<TO>(x[g]);
+        }
+      }
     return;
   }
   const TD* d = branch != nullptr ? branch + static_cast<size_t>(row) * width : nullptr;
-  float held[MAX_PER_THREAD];
+  float held[MAX_PER_THREAD][VEC];
   float sum = 0.f;
 #pragma unroll
   for (int it = 0; it < MAX_PER_THREAD; ++it) {
-    const int i = threadIdx.x + it * blockDim.x;
-    held[it] = 0.f;
-    if (i < width) {
-      held[it] = rows != nullptr ? x[i] : load_sum<TD>(d + i, partial_stride, partials);
-      sum += held[it];
+    const int g = threadIdx.x + it * blockDim.x;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) held[it][e] = 0.f;
+    if (g < groups) {
+      if (VEC == 4) {
+        float v[4];
+        if (rows != nullptr) {
+          load4<float>(x + g * 4, v);
+        } else {
+          load_sum4<TD>(d + g * 4, partial_stride, partials, v);   // the slices of a K-split product, in ascending order
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) held[it][e % VEC] = v[e];
+      } else {
+        held[it][0] = rows != nullptr ? x[g] : load_sum<TD>(d + g, partial_stride, partials);
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) sum += held[it][e];
     }
   }
   float mean = 0.f;
@@ -70,24 +107,46 @@ norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int p
   float sum_sq = 0.f;
 #pragma unroll
   for (int it = 0; it < MAX_PER_THREAD; ++it) {
-    const int i = threadIdx.x + it * blockDim.x;
-    if (i < width) {
-      held[it] -= mean;
-      sum_sq = fmaf(held[it], held[it], sum_sq);
+    const int g = threadIdx.x + it * blockDim.x;
+    if (g < groups) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        held[it][e] -= mean;
+        sum_sq = fmaf(held[it][e], held[it][e], sum_sq);
+      }
     }
   }
   const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / static_cast<float>(width) + eps);
 #pragma unroll
   for (int it = 0; it < MAX_PER_THREAD; ++it) {
-    const int i = threadIdx.x + it * blockDim.x;
-    if (i < width) {
-      float v = __fmul_rn(__fmul_rn(held[it], inv), weight[i]);
-      if (bias != nullptr) v = __fadd_rn(v, bias[i]);
-      if (rows == nullptr) {
-        v = __fadd_rn(x[i], v);
-        x[i] = v;
+    const int g = threadIdx.x + it * blockDim.x;
+    if (g < groups) {
+      if (VEC == 4) {
+        float w[4], b[4] = {0.f, 0.f, 0.f, 0.f}, r[4];
+        load4<float>(weight + g * 4, w);
+        if (bias != nullptr) load4<float>(bias + g * 4, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          r[e] = __fmul_rn(__fmul_rn(held[it][e % VEC], inv), w[e]);
+          if (bias != nullptr) r[e] = __fadd_rn(r[e], b[e]);
+        }
+        if (rows == nullptr) {
+          float before[4];
+          load4<float>(x + g * 4, before);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) r[e] = __fadd_rn(before[e], r[e]);
+          store4<float>(x + g * 4, r);
+        }
+        if (y != nullptr) store4<TO>(y + g * 4, r);
+      } else {
+        float v = __fmul_rn(__fmul_rn(held[it][0], inv), weight[g]);
+        if (bias != nullptr) v = __fadd_rn(v, bias[g]);
+        if (rows == nullptr) {
+          v = __fadd_rn(x[g], v);
+          x[g] = v;
+        }
+        if (y != nullptr) y[g] = from_float<TO>(v);
       }
-      if (y != nullptr) y[i] = from_float<TO>(v);
     }
   }
 }
@@ -96,16 +155,17 @@ norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int p
 // One block per token.  qk [P][n][H * D + G * D] float32.  The keys as projected (before their norm)
 // are the values.  Heads are stored `padded` (>= D) elements apart, the padding zeroed, so that an
 // attention kernel built for the next served head size can read them.
-template <typename T>
+template <typename T, int VEC>
 __global__ void qk_norm_store_kernel(const float* __restrict__ qk, int partials, long long partial_stride,
                                      const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
                                      const int* __restrict__ positions, float temp_coef, int temp_every,
                                      T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      const int* __restrict__ slots, int num_heads, int num_kv_heads, int dim, int padded,
                                      long long num_slots) {
-  extern __shared__ float row_shared[];   // the token's q and k elements
+  extern __shared__ __align__(16) float row_shared[];   // the token's q and k elements
   __shared__ float scratch[33];
   let_dependents_start();
+  // before the wait: what no kernel writes (the step's positions and slots)
   const int token = blockIdx.x;
   const int q_width = num_heads * dim, k_width = num_kv_heads * dim;
   long long slot = -1;
@@ -121,41 +181,64 @@ __global__ void qk_norm_store_kernel(const float* __restrict__ qk, int partials,
   wait_for_previous();
   const float* row = qk + static_cast<size_t>(token) * (q_width + k_width);
   float q_sq = 0.f, k_sq = 0.f;
-  for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x) {
-    const float v = sum_partials(row + i, partial_stride, partials);
-    row_shared[i] = v;
-    if (i < q_width) q_sq = fmaf(v, v, q_sq);
-    else k_sq = fmaf(v, v, k_sq);
+  for (int g = threadIdx.x; g < (q_width + k_width) / VEC; g += blockDim.x) {
+    const int i = g * VEC;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (VEC == 4) {
+      sum_partials4(row + i, partial_stride, partials, v);
+      *reinterpret_cast<float4*>(row_shared + i) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+      v[0] = sum_partials(row + i, partial_stride, partials);
+      row_shared[i] = v[0];
+    }
+    float sq = 0.f;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) sq = fmaf(v[e], v[e], sq);
+    if (i < q_width) q_sq += sq;   // a group never holds elements of both: q_width is a multiple of VEC
+    else k_sq += sq;
   }
   float q_gain = temperature, k_gain = 1.0f;
   if (q_weight != nullptr) q_gain = temperature / sqrtf(block_sum(q_sq, scratch) / static_cast<float>(q_width) + eps);
   if (k_weight != nullptr) k_gain = 1.0f / sqrtf(block_sum(k_sq, scratch) / static_cast<float>(k_width) + eps);
   __syncthreads();
+  const int per_head = padded / VEC;
   T* q_dst = q_out + static_cast<size_t>(token) * num_heads * padded;
-  for (int i = threadIdx.x; i < num_heads * padded; i += blockDim.x) {
-    const int head = i / padded, d = i - head * padded;
-    float v = 0.f;
-    if (d < dim) {
+  for (int g = threadIdx.x; g < num_heads * per_head; g += blockDim.x) {
+    const int head = g / per_head, d = (g - head * per_head) * VEC;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (d < dim) {   // a group is inside the head or all padding: dim is a multiple of VEC
       const int c = head * dim + d;
-      v = row_shared[c] * q_gain;
-      if (q_weight != nullptr) v *= q_weight[c];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        v[e] = row_shared[c + e] * q_gain;
+        if (q_weight != nullptr) v[e] *= q_weight[c + e];
+      }
     }
-    q_dst[i] = from_float<T>(v);
+    if (VEC == 4) store4<T>(q_dst + head * padded + d, v);
+    else q_dst[head * padded + d] = from_float<T>(v[0]);
   }
   if (slot >= 0) {
     T* k_dst = k_cache + static_cast<size_t>(slot) * num_kv_heads * padded;
     T* v_dst = v_cache + static_cast<size_t>(slot) * num_kv_heads * padded;
-    for (int i = threadIdx.x; i < num_kv_heads * padded; i += blockDim.x) {
-      const int head = i / padded, d = i - head * padded;
-      float k = 0.f, v = 0.f;
+    for (int g = threadIdx.x; g < num_kv_heads * per_head; g += blockDim.x) {
+      const int head = g / per_head, d = (g - head * per_head) * VEC;
+      float k[4] = {0.f, 0.f, 0.f, 0.f}, v[4] = {0.f, 0.f, 0.f, 0.f};
       if (d < dim) {
         const int c = head * dim + d;
-        v = row_shared[q_width + c];
-        k = v * k_gain;
-        if (k_weight != nullptr) k *= k_weight[c];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          v[e] = row_shared[q_width + c + e];
+          k[e] = v[e] * k_gain;
+          if (k_weight != nullptr) k[e] *= k_weight[c + e];
+        }
       }
-      k_dst[i] = from_float<T>(k);
-      v_dst[i] = from_float<T>(v);
+      if (VEC == 4) {
+        store4<T>(k_dst + head * padded + d, k);
+        store4<T>(v_dst + head * padded + d, v);
+      } else {
+        k_dst[head * padded + d] = from_float<T>(k[0]);
+        v_dst[head * padded + d] = from_float<T>(v[0]);
+      }
     }
   }
 }
@@ -169,8 +252,8 @@ __global__ void latent_store_kernel(const float* __restrict__ fused, int partial
                                     const float* __restrict__ latent_weight, float eps, T* __restrict__ q_out,
                                     T* __restrict__ latent_cache, const int* __restrict__ slots,
                                     float* __restrict__ gate_out, int q_width, int rank, int padded, int gates,
-                                    long long num_slots) {
-  extern __shared__ float row_shared[];   // the token's latent
+                                    long long num_slots, int vec) {
+  extern __shared__ __align__(16) float row_shared[];   // the token's latent
   __shared__ float scratch[33];
   let_dependents_start();
   const int token = blockIdx.x;
@@ -181,8 +264,16 @@ __global__ void latent_store_kernel(const float* __restrict__ fused, int partial
   }
   wait_for_previous();
   const float* row = fused + static_cast<size_t>(token) * (q_width + rank + gates);
-  for (int i = threadIdx.x; i < q_width; i += blockDim.x)
-    q_out[static_cast<size_t>(token) * q_width + i] = from_float<T>(sum_partials(row + i, partial_stride, partials));
+  if (vec) {   // the queries are the wide part: 16-byte loads, every slice of a K-split product in flight together
+    for (int g = threadIdx.x; g < q_width / 4; g += blockDim.x) {
+      float v[4];
+      sum_partials4(row + g * 4, partial_stride, partials, v);
+      store4<T>(q_out + static_cast<size_t>(token) * q_width + g * 4, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < q_width; i += blockDim.x)
+      q_out[static_cast<size_t>(token) * q_width + i] = from_float<T>(sum_partials(row + i, partial_stride, partials));
+  }
   for (int i = threadIdx.x; i < gates; i += blockDim.x) {
     const float g = sum_partials(row + q_width + rank + i, partial_stride, partials);
     gate_out[static_cast<size_t>(token) * gates + i] = 1.0f / (1.0f + expf(-g));
@@ -203,26 +294,46 @@ __global__ void latent_store_kernel(const float* __restrict__ fused, int partial
   }
 }
 
+// x [n][heads][dim] in place; a thread takes four elements (dim is a multiple of 4), blockIdx.y the token
 template <typename T>
-__global__ void head_scale_kernel(T* __restrict__ x, const float* __restrict__ gate, int heads, int dim) {
+__global__ void head_scale_kernel(T* __restrict__ x, const float* __restrict__ gate, int heads, int dim, int n) {
   let_dependents_start();
   wait_for_previous();
-  const int token = blockIdx.x;
-  T* row = x + static_cast<size_t>(token) * heads * dim;
-  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x)
-    row[i] = from_float<T>(to_float(row[i]) * gate[static_cast<size_t>(token) * heads + i / dim]);
+  const int per_row = heads * dim / 4;
+  for (int token = blockIdx.y; token < n; token += gridDim.y) {
+    T* row = x + static_cast<size_t>(token) * heads * dim;
+    const float* g = gate + static_cast<size_t>(token) * heads;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < per_row; i += gridDim.x * blockDim.x) {
+      float v[4];
+      load4<T>(row + i * 4, v);
+      const float scale = g[i * 4 / dim];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] *= scale;
+      store4<T>(row + i * 4, v);
+    }
+  }
 }
 
 template <typename TD, typename TO>
 static int launch_norm_rows(float* resid, const void* branch, int partials, long long partial_stride, const int* rows,
                             const float* weight, const float* bias, float eps, int layer_norm, void* out, int n, int width,
                             cudaStream_t stream) {
-  int threads = ((width + MAX_PER_THREAD - 1) / MAX_PER_THREAD + 31) / 32 * 32;
-  if (n <= 256) threads = (width + 31) / 32 * 32;   // few rows: latency counts, one element per thread where that fits
+  const uintptr_t addresses = reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(branch) |
+                              reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(bias) |
+                              reinterpret_cast<uintptr_t>(out);
+  const bool vec = width % 4 == 0 && addresses % 16 == 0 && (partials == 1 || partial_stride % 4 == 0);
+  const int groups = vec ? width / 4 : width;
+  // many rows (prompts): bandwidth counts, small blocks whose threads keep several groups in flight;
+  // few rows (decoding): latency counts, one group per thread where a block can hold the row that way
+  int threads = ((groups + (n > 256 ? 3 : 0)) / (n > 256 ? 4 : 1) + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
-  if (static_cast<long long>(threads) * MAX_PER_THREAD < width) return SHRIKE_BAD_ARGUMENT;
-  launch_dependent(norm_rows_kernel<TD, TO>, n, threads, 0, stream, resid, static_cast<const TD*>(branch), partials,
-                   partial_stride, rows, weight, bias, eps, layer_norm, static_cast<TO*>(out), width);
+  if (static_cast<long long>(threads) * MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
+  if (vec)
+    launch_dependent(norm_rows_kernel<TD, TO, 4>, n, threads, 0, stream, resid, static_cast<const TD*>(branch), partials,
+                     partial_stride, rows, weight, bias, eps, layer_norm, static_cast<TO*>(out), width);
+  else
+    launch_dependent(norm_rows_kernel<TD, TO, 1>, n, threads, 0, stream, resid, static_cast<const TD*>(branch), partials,
+                     partial_stride, rows, weight, bias, eps, layer_norm, static_cast<TO*>(out), width);
   return SHRIKE_OK;
 }
 
@@ -267,21 +378,27 @@ SHRIKE_API int shrike_qk_norm_store(const float* qk, int partials, long long par
   if ((k_cache == nullptr) != (v_cache == nullptr)) return SHRIKE_BAD_ARGUMENT;
   const size_t smem = sizeof(float) * static_cast<size_t>(num_heads + num_kv_heads) * dim;
   if (smem > static_cast<size_t>(shrike_device().max_smem)) return SHRIKE_BAD_ARGUMENT;
-#define SHRIKE_QK_CASE(T)                                                                                    \
+  const uintptr_t addresses = reinterpret_cast<uintptr_t>(qk) | reinterpret_cast<uintptr_t>(q_out) |
+                              reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache);
+  const bool vec = dim % 4 == 0 && padded % 4 == 0 && addresses % 16 == 0 && (partials == 1 || partial_stride % 4 == 0);
+  const int threads = n > 256 ? 128 : 256;
+#define SHRIKE_QK_LAUNCH(T, V)                                                                               \
   do {                                                                                                       \
     if (smem > 48 * 1024) {                                                                                  \
-      const cudaError_t err = cudaFuncSetAttribute(qk_norm_store_kernel<T>,                                  \
+      const cudaError_t err = cudaFuncSetAttribute(qk_norm_store_kernel<T, V>,                               \
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
       if (err != cudaSuccess) return static_cast<int>(err);                                                  \
     }                                                                                                        \
-    launch_dependent(qk_norm_store_kernel<T>, n, 256, smem, stream, qk, partials, partial_stride, q_weight,  \
-                     k_weight, eps, positions, temp_coef, temp_every, static_cast<T*>(q_out),                \
+    launch_dependent(qk_norm_store_kernel<T, V>, n, threads, smem, stream, qk, partials, partial_stride,     \
+                     q_weight, k_weight, eps, positions, temp_coef, temp_every, static_cast<T*>(q_out),      \
                      static_cast<T*>(k_cache), static_cast<T*>(v_cache), slots, num_heads, num_kv_heads, dim, \
                      padded, num_slots);                                                                     \
   } while (0)
+#define SHRIKE_QK_CASE(T) do { if (vec) SHRIKE_QK_LAUNCH(T, 4); else SHRIKE_QK_LAUNCH(T, 1); } while (0)
   if (dtype == SHRIKE_F32) SHRIKE_QK_CASE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_QK_CASE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;
+#undef SHRIKE_QK_LAUNCH
 #undef SHRIKE_QK_CASE
   return shrike_launch_status();
 }
@@ -297,10 +414,12 @@ SHRIKE_API int shrike_latent_store(const float* fused, int partials, long long p
   if (gates > 0 && gate_out == nullptr) return SHRIKE_BAD_ARGUMENT;
   const size_t smem = sizeof(float) * static_cast<size_t>(rank);
   if (smem > 48 * 1024) return SHRIKE_BAD_ARGUMENT;
+  const int vec = q_width % 4 == 0 && (q_width + rank + gates) % 4 == 0 && (partials == 1 || partial_stride % 4 == 0) &&
+                  (reinterpret_cast<uintptr_t>(fused) | reinterpret_cast<uintptr_t>(q_out)) % 16 == 0;
 #define SHRIKE_LATENT_CASE(T)                                                                                  \
   launch_dependent(latent_store_kernel<T>, n, 256, smem, stream, fused, partials, partial_stride, latent_weight, \
                    eps, static_cast<T*>(q_out), static_cast<T*>(latent_cache), slots, gate_out, q_width, rank,  \
-                   padded, gates, num_slots)
+                   padded, gates, num_slots, vec)
   if (dtype == SHRIKE_F32) SHRIKE_LATENT_CASE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_LATENT_CASE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;
@@ -311,10 +430,12 @@ SHRIKE_API int shrike_latent_store(const float* fused, int partials, long long p
 SHRIKE_API int shrike_head_scale(void* x, const float* gate, int dtype, int n, int heads, int dim, cudaStream_t stream) {
   using namespace branch;
   if (n <= 0) return SHRIKE_OK;
-  if (heads <= 0 || dim <= 0) return SHRIKE_BAD_ARGUMENT;
-  if (dtype == SHRIKE_F32) launch_dependent(head_scale_kernel<float>, n, 256, 0, stream, static_cast<float*>(x), gate, heads, dim);
+  if (heads <= 0 || dim <= 0 || dim % 4 || reinterpret_cast<uintptr_t>(x) % 16) return SHRIKE_BAD_ARGUMENT;
+  const int per_row = heads * dim / 4;
+  const dim3 grid(max(1, min(8, (per_row + 255) / 256)), max(1, min(n, 65535)));
+  if (dtype == SHRIKE_F32) launch_dependent(head_scale_kernel<float>, grid, 256, 0, stream, static_cast<float*>(x), gate, heads, dim, n);
   else if (dtype == SHRIKE_BF16)
-    launch_dependent(head_scale_kernel<__nv_bfloat16>, n, 256, 0, stream, static_cast<__nv_bfloat16*>(x), gate, heads, dim);
+    launch_dependent(head_scale_kernel<__nv_bfloat16>, grid, 256, 0, stream, static_cast<__nv_bfloat16*>(x), gate, heads, dim, n);
   else return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
 }

@@ -50,6 +50,30 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
   return __float2bfloat16_rn(v);
 }
 
+// Four consecutive elements as float32, with one 16-byte (float32) or 8-byte (bfloat16) access.
+template <typename TD> __device__ __forceinline__ void load4(const TD* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+  v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+}
+template <typename TO> __device__ __forceinline__ void store4(TO* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<const unsigned*>(&lo);
+  t.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
 // Programmatic dependent launch.  Every kernel of this package is launched so that it may
 // start while the kernel before it on the stream is still running (its launch latency and
 // set-up are hidden that way), and every kernel begins with
@@ -145,6 +169,24 @@ __device__ __forceinline__ float sum_partials(const float* base, long long strid
     if (i < partials) sum = __fadd_rn(sum, held[i]);
   for (int i = 16; i < partials; ++i) sum = __fadd_rn(sum, base[i * stride]);
   return sum;
+}
+
+// The same for four consecutive elements with 16-byte loads: v = base[0..3] + base[stride + 0..3] + ...,
+// up to eight slices in flight before the first addition, added in ascending order.
+__device__ __forceinline__ void sum_partials4(const float* base, long long stride, int partials, float (&v)[4]) {
+  load4<float>(base, v);
+  for (int first = 1; first < partials; first += 7) {
+    float more[7][4];
+#pragma unroll
+    for (int q = 0; q < 7; ++q)
+      if (first + q < partials) load4<float>(base + (first + q) * stride, more[q]);
+#pragma unroll
+    for (int q = 0; q < 7; ++q)
+      if (first + q < partials) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = __fadd_rn(v[e], more[q][e]);
+      }
+  }
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -70,29 +70,6 @@ SHRIKE_API int shrike_embed(const int* ids, const void* table, int table_dtype, 
 // row is read once; VEC = 4 uses 16-byte accesses (width a multiple of 4).
 constexpr int NORM_MAX_PER_THREAD = 8;  // elements (VEC = 1) or float4 groups (VEC = 4) a thread may hold
 
-template <typename TD> __device__ __forceinline__ void load4(const TD* p, float (&v)[4]);
-template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
-  const float4 t = *reinterpret_cast<const float4*>(p);
-  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-}
-template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
-  const uint2 t = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
-  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
-  v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
-}
-template <typename TO> __device__ __forceinline__ void store4(TO* p, const float (&v)[4]);
-template <> __device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-}
-template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
-  uint2 t;
-  t.x = *reinterpret_cast<const unsigned*>(&lo);
-  t.y = *reinterpret_cast<const unsigned*>(&hi);
-  *reinterpret_cast<uint2*>(p) = t;
-}
-
 // `delta` may be a stack of `partials` arrays (the slices of a K-split matrix product),
 // `partial_stride` elements apart; they are added in ascending order.
 // PER_THREAD 1 (few rows of up to 1024 groups): a thread holds one group, reads the norm weight
@@ -311,7 +288,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 // whole run pair, 64 contiguous bytes in and 32 out, so a warp reads 2 KiB in one piece.  (With a
 // thread per 16-byte group the gate loads of a warp touch every other 32 bytes, the up loads the
 // rest: the same bytes, twice the lines per instruction.)
-__global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, int rows) {
+__global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, int rows, int act) {
   let_dependents_start();
   wait_for_previous();
   const int runs_per_row = inter / 16;
@@ -330,7 +307,7 @@ __global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up
         uint4 packed;
         __nv_bfloat16* r = reinterpret_cast<__nv_bfloat16*>(&packed);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) r[j] = from_float<__nv_bfloat16>(silu_times<__nv_bfloat16>(to_float(g[j]), to_float(u[j])));
+        for (int j = 0; j < 8; ++j) r[j] = from_float<__nv_bfloat16>(act_times<__nv_bfloat16>(act, to_float(g[j]), to_float(u[j])));
         out_row[run * 2 + half] = packed;
       }
     }
@@ -339,12 +316,12 @@ __global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up
 
 template <typename T>
 static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, int block, int act, cudaStream_t stream) {
-  if (act == SHRIKE_ACT_SILU && sizeof(T) == 2 && block == 16 && inter % 16 == 0 &&
+  if (sizeof(T) == 2 && block == 16 && inter % 16 == 0 &&
       (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
     const int threads = 256, runs_per_row = inter / 16;
     const dim3 grid(max(1, min(64, (runs_per_row + threads - 1) / threads)), max(1, min(n, 65535)));
     launch_dependent(silu_mul_runs16_kernel, grid, threads, 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
-                     static_cast<__nv_bfloat16*>(out), inter, n);
+                     static_cast<__nv_bfloat16*>(out), inter, n, act);
     return;
   }
   constexpr int WIDE = 16 / sizeof(T);

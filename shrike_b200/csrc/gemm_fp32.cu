@@ -9,16 +9,11 @@ constexpr int GEMM_THREADS = 256;
 
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
-                 float* __restrict__ C, int M, int N, int K, int vec_ok, long long lda, long long ldc,
-                 long long a_batch, long long w_batch, long long c_batch) {
+                 float* __restrict__ C, int M, int N, int K, int vec_ok) {
   __shared__ __align__(16) float a_tile[BK][BM + 4];
   __shared__ __align__(16) float w_tile[BK][BN + 4];
   let_dependents_start();
   wait_for_previous();
-  // blockIdx.z: one product of a batch (the heads of a per-head projection), each with its own matrix
-  A += blockIdx.z * a_batch;
-  W += blockIdx.z * w_batch;
-  C += blockIdx.z * c_batch;
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int load_row = tid >> 2, load_k = (tid & 3) * 4;
@@ -34,7 +29,7 @@ gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const
     const int k = k0 + load_k;
     const int am = m0 + load_row, wn = n0 + load_row;
     if (am < M) {
-      const float* src = A + static_cast<size_t>(am) * lda + k;
+      const float* src = A + static_cast<size_t>(am) * K + k;
       if (vec_ok && k + 3 < K) {
         const float4 v = *reinterpret_cast<const float4*>(src);
         a_reg[0] = v.x; a_reg[1] = v.y; a_reg[2] = v.z; a_reg[3] = v.w;
@@ -78,7 +73,7 @@ gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < N) C[static_cast<size_t>(m) * ldc + n] = bias ? acc[i][j] + bias[n] : acc[i][j];
+      if (n < N) C[static_cast<size_t>(m) * N + n] = bias ? acc[i][j] + bias[n] : acc[i][j];
     }
   }
 }
@@ -91,23 +86,6 @@ SHRIKE_API int shrike_gemm_fp32(const float* A, const float* W, const float* bia
   if (grid.y > 65535) return SHRIKE_BAD_ARGUMENT;
   const int vec_ok = (K % 4 == 0) && (reinterpret_cast<uintptr_t>(A) % 16 == 0) &&
                      (reinterpret_cast<uintptr_t>(W) % 16 == 0);
-  gemm_fp32_kernel<<<grid, GEMM_THREADS, 0, stream>>>(A, W, bias, C, M, N, K, vec_ok, K, N, 0, 0, 0);
-  return shrike_launch_status();
-}
-
-// `heads` products at once, one matrix each: C_h[M,N] = A_h[M,K] * W_h[N,K]^T, where head h's rows of A start
-// `a_head` elements after those of head h - 1 and lie `lda` apart (likewise C with `c_head`, `ldc`), and W is
-// [heads, N, K].  A [tokens, heads, K] array has lda = heads * K and a_head = K.  The same sum order as above.
-SHRIKE_API int shrike_gemm_fp32_heads(const float* A, const float* W, float* C, int M, int N, int K, int heads,
-                                      long long lda, long long a_head, long long ldc, long long c_head,
-                                      cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || heads <= 0) return SHRIKE_OK;
-  if (K <= 0 || heads > 65535) return SHRIKE_BAD_ARGUMENT;
-  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, heads);
-  if (grid.y > 65535) return SHRIKE_BAD_ARGUMENT;
-  const int vec_ok = (K % 4 == 0) && (lda % 4 == 0) && (a_head % 4 == 0) && (reinterpret_cast<uintptr_t>(A) % 16 == 0) &&
-                     (reinterpret_cast<uintptr_t>(W) % 16 == 0);
-  gemm_fp32_kernel<<<grid, GEMM_THREADS, 0, stream>>>(A, W, nullptr, C, M, N, K, vec_ok, lda, ldc, a_head,
-                                                      static_cast<long long>(N) * K, c_head);
+  gemm_fp32_kernel<<<grid, GEMM_THREADS, 0, stream>>>(A, W, bias, C, M, N, K, vec_ok);
   return shrike_launch_status();
 }

@@ -132,13 +132,11 @@ class CudaOps:
         lib.shrike_qk_norm_store.argtypes = [_P, _I, _LL, _P, _P, _F, _P, _F, _I, _P, _P, _P, _P] + [_I] * 6 + [_LL, _P]
         lib.shrike_latent_store.argtypes = [_P, _I, _LL, _P, _F, _P, _P, _P, _P] + [_I] * 6 + [_LL, _P]
         lib.shrike_head_scale.argtypes = [_P, _P, _I, _I, _I, _I, _P]
-        lib.shrike_gemm_fp32_heads.argtypes = [_P, _P, _P, _I, _I, _I, _I, _LL, _LL, _LL, _LL, _P]
         lib.shrike_sample_slices.argtypes = [_I]
         lib.shrike_sample_slices.restype = _I
         for name in ("shrike_embed", "shrike_add_rmsnorm", "shrike_silu_mul", "shrike_rope_kv_write",
                      "shrike_kv_write", "shrike_gemm_fp32", "shrike_sample", "shrike_embed_positions", "shrike_act_mul",
-                     "shrike_norm_rows", "shrike_qk_norm_store", "shrike_latent_store", "shrike_head_scale",
-                     "shrike_gemm_fp32_heads"):
+                     "shrike_norm_rows", "shrike_qk_norm_store", "shrike_latent_store", "shrike_head_scale"):
             getattr(lib, name).restype = _I
 
     def _attention_lib(self, head_dim: int):
@@ -166,6 +164,10 @@ class CudaOps:
                 [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _P]
             )
             lib.shrike_paged_attention_tc_portions.restype = _I
+            lib.shrike_paged_attention_tc_portions_scores.argtypes = (
+                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P]
+            )
+            lib.shrike_paged_attention_tc_portions_scores.restype = _I
             lib.shrike_attention_tc_portions_rows.restype = _I
             lib.shrike_attention_tc_portions_splits.argtypes = [_I, _I, _I, _I, _I]
             lib.shrike_attention_tc_portions_splits.restype = _I
@@ -320,27 +322,6 @@ class CudaOps:
         _check(self.core.shrike_head_scale(_ptr(x), _ptr(gate), self.code, x.shape[0], heads, dim, self._stream()),
                "head_scale")
 
-    def head_linear(self, x, w, out):
-        """A product per head: out[n, h, :] = w[h] @ x[n, h, :] for x [N, H, I], w [H, O, I], out [N, H, O].
-        float32 runs this package's FFMA kernel once per head in one launch; bfloat16 is a batched library
-        product (float32 accumulation) written straight into `out`."""
-        n, heads, inner = x.shape
-        outer = w.shape[1]
-        if tuple(w.shape) != (heads, outer, inner) or tuple(out.shape) != (n, heads, outer):
-            raise KernelError(f"head_linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-        _dense(x, self.dtype, "head_linear input")
-        _dense(w, self.dtype, "head_linear weight")
-        _dense(out, self.dtype, "head_linear output")
-        if self.dtype == torch.float32:
-            self.launches += 1
-            _check(self.core.shrike_gemm_fp32_heads(_ptr(x), _ptr(w), _ptr(out), n, outer, inner, heads,
-                                                    heads * inner, inner, heads * outer, outer, self._stream()),
-                   "gemm_fp32_heads")
-            return out
-        self.library_calls += 1
-        torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
-        return out
-
     def linear(self, x, w, out, bias=None, allow_partials=False):
         """x[N, K] @ w[O, K]^T (+ bias) into `out` [N, O] (float32 or the activation type).
 
@@ -492,22 +473,21 @@ class CudaOps:
                 page_size, num_pages, scale, window or 0, softcap or 0.0, _ptr(slopes), _ptr(out), self._stream()),
                 "paged_attention")
             return
-        modified = bool(softcap) or slopes is not None
         if slopes is not None:
             _dense(slopes, torch.float32, "distance slopes")
             if slopes.numel() != num_heads:
                 raise KernelError("one distance slope per query head")
         plan = self.attention_plan(num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
-                                   q.shape[0], q_lens, modified)
+                                   q.shape[0], q_lens)
         self.launches += plan.has_single + plan.has_portions + (1 if plan.portion_splits > 1 else 0)
         has_portions = plan.has_portions
         if plan.tc_portions:
-            _check(lib.shrike_paged_attention_tc_portions(
+            _check(lib.shrike_paged_attention_tc_portions_scores(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
                 q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
                 plan.has_single, max_q_len, _ptr(self.status), plan.portion_splits, _ptr(plan.portion_scratch),
                 self.portion_tiles(q_lens, plan.has_single, lib.shrike_attention_tc_portions_rows()), _ptr(seq_of_token),
-                self._stream()), "paged_attention_tc_portions")
+                softcap or 0.0, _ptr(slopes), self._stream()), "paged_attention_tc_portions")
             has_portions = 0
             if not plan.has_single:
                 return
@@ -530,7 +510,7 @@ class CudaOps:
         return tiles
 
     def attention_plan(self, num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
-                       num_tokens=0, q_lens=None, modified_scores=False):
+                       num_tokens=0, q_lens=None):
         """How a bfloat16 batch's attention is cut: which kernels run (single tokens, portions, the
         tensor-core form of the latter), the key splits and clusters of the single-token kernel, the
         key splits of the portions kernel, and their scratch.  A function of the batch's shape alone."""
@@ -554,9 +534,8 @@ class CudaOps:
                 self._arrivals = torch.zeros(max(groups, 4096), dtype=torch.int32, device=self.device)
                 self.generation += 1
             scratch, arrivals = self._scratch, self._arrivals
-        # scores with a soft cap or a distance bias go through the mma.sync kernels, which apply them
         tc_portions = bool(has_portions and self.tensor_core_attention and lib.shrike_attention_tc_available()
-                           and page_size in (8, 16, 32, 64) and not modified_scores)
+                           and page_size in (8, 16, 32, 64))
         portion_splits, portion_scratch = 1, None
         if tc_portions and num_tokens > 0:
             tiles = self.portion_tiles(q_lens, has_single, lib.shrike_attention_tc_portions_rows())

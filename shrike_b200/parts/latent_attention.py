@@ -5,14 +5,18 @@ pages).  Head h's keys and values are k = Wuk_h c and v = Wuv_h c, its score sca
 k nor v is ever formed for a cached token: the key projection is moved to the query and the value
 projection to the output,
 
-    q_h . (Wuk_h c_j) = (Wuk_h^T q_h) . c_j        sum_j p_j Wuv_h c_j = Wuv_h (sum_j p_j c_j),
+    (Wq_h x) . (Wuk_h c_j) = (Wuk_h^T Wq_h x) . c_j      Wo_h sum_j p_j Wuv_h c_j = (Wo_h Wuv_h) sum_j p_j c_j,
 
 so the layer is attention with ONE key/value head of size `latent_rank` whose keys and values are
-the same cached rows, between two small per-head products; it runs on the engine's paged attention
-kernels as they are.  A layer without a latent of its own reads the pages another layer's run wrote
-(the run order names the cache) with its own Wuk, Wuv, queries and output.  An optional gate
-multiplies head h's output by sigmoid(Wg x)_h; it is applied to the attended latent, before the
-value projection, which is linear.  Query, latent and gate come from one fused product.
+the same cached rows, and it runs on the engine's paged attention kernels as they are.  The two
+products of matrices are formed once, when the weights are loaded (in float32, then kept in the
+engine's type): the query projection becomes [heads * rank, width] and the output projection
+[width, heads * rank].  With rank = 2 * dim that is twice the weights and products of the two
+projections, about 1 % of a layer's; in exchange a step has no per-head products at all.  A layer
+without a latent of its own reads the pages another layer's run wrote (the run order names the
+cache) with its own Wuk, Wuv, queries and output.  An optional gate multiplies head h's output by
+sigmoid(Wg x)_h; it is applied to the attended latent, which the output projection takes linearly.
+Query, latent and gate come from one fused product.
 """
 
 from __future__ import annotations
@@ -50,7 +54,20 @@ class LatentAttention:
         heads, dim, vdim, rank = spec.num_heads, spec.head_dim, spec.value_dim, spec.latent_rank
         self.padded = padded_head(rank)
         ops.check_head_dim(self.padded)
-        rows = [tensors.pop("q_proj.weight")]
+        k_up = tensors.pop("k_up.weight").float().view(heads, dim, rank)
+        v_up = tensors.pop("v_up.weight").float().view(heads, vdim, rank)
+        w_q = tensors.pop("q_proj.weight")
+        w_o = tensors.pop("o_proj.weight")
+        kept = w_q.dtype
+        # queries straight into the latent space: rows [h * padded + r] = sum_d Wuk[h, d, r] Wq[h * dim + d, :]
+        absorbed = torch.zeros(heads, self.padded, spec.width, dtype=torch.float32, device=w_q.device)
+        absorbed[:, :rank] = torch.einsum("hdr,hdw->hrw", k_up, w_q.float().view(heads, dim, spec.width))
+        rows = [absorbed.view(heads * self.padded, spec.width).to(kept)]
+        # the attended latent straight to the residual's width: columns [h * padded + r] = Wo[:, h, :] Wuv[h, :, r]
+        expanded = torch.zeros(spec.width, heads, self.padded, dtype=torch.float32, device=w_o.device)
+        expanded[:, :, :rank] = torch.einsum("whv,hvr->whr", w_o.float().view(spec.width, heads, vdim), v_up)
+        self.w_o = expanded.view(spec.width, heads * self.padded).to(kept).contiguous()
+        del absorbed, expanded
         self.latent_weight = None
         if spec.own_latent:
             rows.append(tensors.pop("kv_down.weight"))
@@ -58,20 +75,12 @@ class LatentAttention:
         if spec.gated:
             rows.append(tensors.pop("gate.weight"))
         self.w_in = torch.cat(rows).contiguous()
-        k_up, v_up = tensors.pop("k_up.weight"), tensors.pop("v_up.weight")
-        # per head: [padded rank, dim] takes a query to the latent space, [vdim, padded rank] brings the
-        # attended latent back; the padding columns and rows are zero
-        self.w_absorb = k_up.new_zeros(heads, self.padded, dim)
-        self.w_absorb[:, :rank] = k_up.view(heads, dim, rank).transpose(1, 2)
-        self.w_expand = v_up.new_zeros(heads, vdim, self.padded)
-        self.w_expand[:, :, :rank] = v_up.view(heads, vdim, rank)
-        self.w_o = tensors.pop("o_proj.weight").contiguous()
-        self.q_width = heads * dim
+        self.q_width = heads * self.padded
         self.in_width = self.w_in.shape[0]
 
     def forward(self, x, ctx, run):
         spec, rt, ops = self.spec, self.runtime, self.ops
-        heads, dim, vdim, padded = spec.num_heads, spec.head_dim, spec.value_dim, self.padded
+        heads, padded = spec.num_heads, self.padded
         n = x.shape[0]
         fused = rt.buffer("qkv", (n, self.in_width), torch.float32)
         fused = ops.linear(x, self.w_in, fused, allow_partials=True)
@@ -82,20 +91,16 @@ class LatentAttention:
         writes = spec.own_latent and run.writes_cache
         ops.latent_store(fused, self.latent_weight, spec.eps, q, latents if writes else None, view.slot_mapping, gate,
                          self.q_width, spec.latent_rank if spec.own_latent else 0, padded, heads if spec.gated else 0)
-        q_latent = rt.buffer("q_latent", (n, heads, padded), rt.act_dtype)
-        ops.head_linear(q.view(n, heads, dim), self.w_absorb, q_latent)
-        attended = rt.buffer("attn_out", (n, heads * padded), rt.act_dtype)
+        attended = rt.buffer("attn_out", (n, self.q_width), rt.act_dtype)
         ops.paged_attention(
-            q_latent.view(n, heads * padded), latents, latents, view.block_table, ctx.q_start, ctx.ctx_len,
-            ctx.seq_of_token, heads, 1, padded, spec.scale, None, attended,
+            q, latents, latents, view.block_table, ctx.q_start, ctx.ctx_len, ctx.seq_of_token,
+            heads, 1, padded, spec.scale, None, attended,
             max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, min_q_len=ctx.min_q_len, q_lens=ctx.q_lens,
         )
         if spec.gated:
             ops.head_scale(attended, gate, heads, padded)
-        out = rt.buffer("head_out", (n, heads, vdim), rt.act_dtype)
-        ops.head_linear(attended.view(n, heads, padded), self.w_expand, out)
         delta = rt.buffer("mixer_delta", (n, spec.width), torch.float32)
-        return ops.linear(out.view(n, heads * vdim), self.w_o, delta, allow_partials=True)
+        return ops.linear(attended, self.w_o, delta, allow_partials=True)
 
 
 register_part("mixer", "latent_attention", LatentAttention)

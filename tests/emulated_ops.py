@@ -94,10 +94,6 @@ class EmulatedOps:
         n = x.shape[0]
         x.copy_((x.float().view(n, heads, dim) * gate[:, :, None]).view(n, -1).to(x.dtype))
 
-    def head_linear(self, x, w, out):
-        out.copy_(torch.einsum("nhi,hoi->nho", x.float(), w.float()).to(out.dtype))
-        return out
-
     def add_rmsnorm(self, resid, delta, weight, eps, out):
         if delta is not None:
             resid.add_(delta.float().sum(0) if delta.dim() == 3 else delta.float())

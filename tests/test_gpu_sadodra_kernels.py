@@ -1,7 +1,7 @@
 """Each mechanism of the Sadodra parts alone on the GPU, against the plain functions of
 `tests/plain/plain_sadodra.py` in float64: the norm on a branch's output, the position embedding,
 the GELU gate (alone and in the tensor-core product's epilogue), queries and keys normed over the
-whole projection with the query temperature, the latent with its gate, the per-head products, and
+whole projection with the query temperature, the latent with its gate, and
 paged attention with soft cap, distance bias and window, with inputs crafted so that one key just
 inside or just outside a window, at a page's border or far back decides the result."""
 
@@ -186,17 +186,15 @@ def test_latent_is_normed_into_its_pages_and_the_gate_is_a_sigmoid(dtype, q_widt
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,heads,inner,outer", [(1, 4, 16, 48), (70, 3, 48, 24), (5, 6, 64, 64), (130, 2, 40, 8)])
-def test_per_head_products_and_head_scale(dtype, n, heads, inner, outer):
+@pytest.mark.parametrize("n,heads,dim", [(1, 4, 48), (70, 3, 16), (2100, 12, 256)])
+def test_head_scale(dtype, n, heads, dim):
     ops = cuda_ops(dtype)
-    x, w = rnd(n, heads, inner, seed=1).to(dtype), rnd(heads, outer, inner, seed=2, scale=0.3).to(dtype)
-    out = torch.empty(n, heads, outer, dtype=dtype, device=DEV)
-    ops.head_linear(x.to(DEV), w.to(DEV), out)
-    close(out, torch.einsum("nhi,hoi->nho", x.double(), w.double()), 2e-5 if dtype == torch.float32 else 8e-2, "per-head product")
+    x = rnd(n, heads * dim, seed=1).to(dtype)
     gate = torch.rand(n, heads, generator=torch.Generator().manual_seed(3))
-    scaled = out.clone().view(n, heads * outer)
-    ops.head_scale(scaled, gate.to(DEV), heads, outer)
-    close(scaled.view(n, heads, outer), out.double().cpu() * gate.double()[:, :, None], 1e-6 if dtype == torch.float32 else 3e-2, "head scale")
+    scaled = x.clone().to(DEV)
+    ops.head_scale(scaled, gate.to(DEV), heads, dim)
+    close(scaled.view(n, heads, dim), x.double().view(n, heads, dim) * gate.double()[:, :, None],
+          1e-6 if dtype == torch.float32 else 3e-2, "head scale")
 
 
 # ------------------------------------------------------------------ paged attention with changed scores
@@ -264,6 +262,25 @@ def test_capped_and_biased_scores_in_single_tokens_and_portions(dtype, heads, kv
     singles = [(q, k, v, 1) for q, k, v, _ in sequences]     # the single-token kernel alone (other split and cluster shapes)
     got, want = attend_both(ops, dtype, singles, page, heads, kv_heads, dim, dim ** -0.5 * 2, window, softcap, slopes)
     close(got, want, TOL[dtype], "single tokens only")
+
+
+@pytest.mark.parametrize("tensor_core,splits", [(True, 0), (True, 3), (False, 0)])
+@pytest.mark.parametrize("heads,kv_heads,dim,page,window,softcap", [(6, 2, 64, 16, 150, 20.0), (4, 1, 128, 16, None, 9.0), (2, 2, 128, 8, 300, None),
+                                                                    (3, 3, 64, 32, 64, 4.0)])
+def test_capped_and_biased_scores_on_the_tensor_core_portions_kernel(heads, kv_heads, dim, page, window, softcap, tensor_core, splits):
+    """Head sizes 64 and 128 take the tcgen05 kernel for portions: with and without it, and with a
+    query tile's keys shared by several CTAs, the same scores."""
+    ops = cuda_ops(torch.bfloat16)
+    ops.tensor_core_attention, ops.portion_splits = tensor_core, splits
+    slopes = ps.distance_slopes(heads, torch.float64)
+    sequences = []
+    for s, (ctx, q_len) in enumerate([(700, 700), (130, 1), (500, 129), (300, 300), (64, 2), (1000, 37)]):
+        g = torch.Generator().manual_seed(70 + s)
+        sequences.append((torch.randn(ctx, heads, dim, generator=g), torch.randn(ctx, kv_heads, dim, generator=g),
+                          torch.randn(ctx, kv_heads, dim, generator=g), q_len))
+    got, want = attend_both(ops, torch.bfloat16, sequences, page, heads, kv_heads, dim, dim ** -0.5 * 3, window, softcap, slopes)
+    ops.check_status()
+    close(got, want, TOL[torch.bfloat16], "portions on the tensor cores")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
