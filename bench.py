@@ -549,8 +549,26 @@ def run_case(args) -> dict:
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3)
         work = {"bytes": n * k * 2}
-    elif args.case in ("attention_single", "attention_portions"):
-        single = args.case == "attention_single"
+    elif args.case == "branch_norm":
+        # resid += LN(branch) and the sum in bfloat16, rows of 7B width: --batch rows (16,384 rows: inputs beyond L2)
+        rows = tokens
+        resid = torch.randn(rows, h, device=dev, dtype=torch.float32)
+        branch = torch.randn(rows, h, device=dev, dtype=torch.float32)
+        weight, bias = torch.ones(h, device=dev), torch.zeros(h, device=dev)
+        out = torch.empty(rows, h, device=dev, dtype=torch.bfloat16)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.norm_add(resid, branch, weight, bias, 1e-6, out)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        work = {"bytes": rows * h * (4 + 4 + 4 + 2)}
+    elif args.case in ("attention_single", "attention_portions", "attention_single_scores", "attention_portions_scores"):
+        single = args.case.startswith("attention_single")
+        changed = args.case.endswith("_scores")   # a soft cap and a distance bias on every score
+        softcap = 50.0 if changed else None
+        slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / heads) for i in range(heads)], device=dev) if changed else None
         seqs = tokens if single else 1
         ctx_len = CONTEXT if single else args.prefill_tokens
         q_len = 1 if single else args.prefill_tokens
@@ -570,7 +588,7 @@ def run_case(args) -> dict:
             keep_busy()
             start.record()
             ops.paged_attention(q, keys, values, table, q_start, ctx, seq_of, heads, kv, d, d ** -0.5, None, out,
-                                max_q_len=q_len, min_q_len=q_len, q_lens=[q_len] * seqs)
+                                max_q_len=q_len, min_q_len=q_len, q_lens=[q_len] * seqs, softcap=softcap, slopes=slopes)
             stop.record()
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3)
@@ -780,9 +798,7 @@ def run_design(args) -> dict:
         torch.cuda.synchronize()
         decode_ms = start.elapsed_time(stop) / args.steps
         launches = (engine.ops.launches - launches) // args.steps
-        runner.use_graphs = False   # kernel by kernel, so that the records name every kernel of the step
-        decode_step()
-        decode_kernels = kernels_of(decode_step)
+        decode_kernels = kernels_of(decode_step)   # a replayed launch sequence: the records name its kernels all the same
         weight_bytes = engine.runner.model.weight_bytes()
         cache_bytes = runner.bytes_per_page / BLOCK_SIZE
         result = {
@@ -851,7 +867,8 @@ def main():
                         help="--case design: the widths at which the Sadodra decoder and the Qwen2 decoder are compared")
     parser.add_argument("--case", default=None,
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
-                             "gemm_qkv, attention_single, attention_portions; --batch gives tokens / sequences.  timeline: per-kernel "
+                             "gemm_qkv, attention_single, attention_portions (with _scores: soft-capped and distance-biased), "
+                             "branch_norm; --batch gives tokens / sequences / rows.  timeline: per-kernel "
                              "times inside one captured decode step (--layers, default 6).  design: the Sadodra decoder "
                              "beside the Qwen2 decoder of equal widths (--design), prefill and decode")
     args = parser.parse_args()

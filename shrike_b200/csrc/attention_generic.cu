@@ -11,14 +11,15 @@
 // Two optional changes to a score s = scale * q.k, in this order: a soft cap, s <- cap * tanh(s / cap)
 // (softcap > 0), and a distance bias, s <- s - slopes[head] * (p - j) for key j (slopes != null).
 //
-// Built once per head size: -DSHRIKE_HEAD_DIM=<multiple of 16, at most 256>.
+// Built once per head size: -DSHRIKE_HEAD_DIM=<multiple of 16, at most 1024>.  Head sizes above 256 (a wide
+// cached latent) have this kernel alone, in bfloat16 too.
 #include "common.cuh"
 
 #ifndef SHRIKE_HEAD_DIM
 #error "compile with -DSHRIKE_HEAD_DIM=<head size>"
 #endif
-static_assert(SHRIKE_HEAD_DIM % 16 == 0 && SHRIKE_HEAD_DIM >= 16 && SHRIKE_HEAD_DIM <= 256,
-              "head size must be a multiple of 16 in [16, 256]");
+static_assert(SHRIKE_HEAD_DIM % 16 == 0 && SHRIKE_HEAD_DIM >= 16 && SHRIKE_HEAD_DIM <= 1024,
+              "head size must be a multiple of 16 in [16, 1024]");
 
 constexpr int D = SHRIKE_HEAD_DIM;
 constexpr int WARPS = 4;

@@ -103,6 +103,12 @@ __device__ __forceinline__ unsigned long long add_pair(unsigned long long a, uns
   return d;
 }
 
+__device__ __forceinline__ float fast_reciprocal(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct Args {
   const int* block_table;
   const int* q_start;
@@ -440,18 +446,23 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_arrive(&sh->s_read[chain]);    // the scores are in registers: their columns may take the next step
       const int key_base = tile_lo * KEYS + h * HALF_KEYS;
       if (modified) {
-        // the scores leave here as the softmax takes them (times log2 e): the scale below is then 1.
-        // tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1) with the hardware exponential and reciprocal
-        // (absolute error about 1e-7, far below what bfloat16 queries and keys leave in a score)
+        // The scores leave here as the softmax takes them (times log2 e): the scale below is then 1.
+        // With s = scale * dot, tanh(s / cap) = 1 - 2 / (2^(2 s log2 e / cap) + 1) (hardware exponential and
+        // reciprocal: absolute error about 1e-7, far below what bfloat16 queries and keys leave in a score),
+        // and key j of this step lies last - key_base - j behind the query.  Per score that is a product, the
+        // two special functions, a sum and two multiply-adds: the softmax threads are bound by instruction issue.
+        const float cap_l2 = args.softcap * LOG2E, slope_l2 = slope * LOG2E;
         const float cap_in = args.softcap > 0.f ? 2.0f * LOG2E * args.scale / args.softcap : 0.f;
+        const float at_zero = (args.softcap > 0.f ? cap_l2 : 0.f) - slope_l2 * static_cast<float>(last - key_base);
 #pragma unroll
         for (int g = 0; g < 2; ++g)
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            float sc = __uint_as_float(v[g][j]);
-            if (args.softcap > 0.f) sc = args.softcap * (1.0f - __fdividef(2.0f, fast_exp2(sc * cap_in) + 1.0f));
-            else sc *= args.scale;
-            sc = (sc - slope * static_cast<float>(last - (key_base + g * 32 + j))) * LOG2E;
+            const float bias = fmaf(static_cast<float>(g * 32 + j), slope_l2, at_zero);   // the index is a constant
+            const float dot = __uint_as_float(v[g][j]);
+            float sc;
+            if (args.softcap > 0.f) sc = fmaf(fast_reciprocal(fast_exp2(dot * cap_in) + 1.0f), -2.0f * cap_l2, bias);
+            else sc = fmaf(dot, args.scale_log2, bias);
             v[g][j] = __float_as_uint(sc);
           }
       }

@@ -51,19 +51,45 @@ template <> __device__ __forceinline__ float load_sum<__nv_bfloat16>(const __nv_
 //   rows != nullptr: out[r] = norm(resid[rows[r]]); nothing else is written.
 // norm(v) = (v - mean) / sqrt(var + eps) * w + b with var the mean squared deviation (layer_norm), or
 // v / sqrt(mean(v^2) + eps) * w (+ b).
-template <typename TD, typename TO, int VEC>
+// PT: groups a thread may hold.  PT <= 2 (few rows, decoding: latency counts) reads the norm's weight and bias
+// before the wait (no kernel writes them) and has the residual and the branch's slices in flight together, so
+// that the row costs one memory round trip; PT = 8 (many rows: bandwidth counts) reads them where it needs them.
+template <typename TD, typename TO, int VEC, int PT>
 __global__ void __launch_bounds__(1024, 1)
 norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int partials, long long partial_stride,
                  const int* __restrict__ rows, const float* __restrict__ weight, const float* __restrict__ bias,
                  float eps, int layer_norm, TO* __restrict__ out, int width) {
   __shared__ float scratch[33];
+  constexpr bool EARLY = PT <= 2;
   let_dependents_start();
+  const int groups = width / VEC;
+  float gain[EARLY ? PT : 1][VEC], shift[EARLY ? PT : 1][VEC];
+  if (EARLY && weight != nullptr) {
+#pragma unroll
+    for (int it = 0; it < (EARLY ? PT : 0); ++it) {
+      const int g = threadIdx.x + it * blockDim.x;
+      if (g < groups) {
+        if (VEC == 4) {
+          float w[4], b[4] = {0.f, 0.f, 0.f, 0.f};
+          load4<float>(weight + g * 4, w);
+          if (bias != nullptr) load4<float>(bias + g * 4, b);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            gain[EARLY ? it : 0][e % VEC] = w[e];
+            shift[EARLY ? it : 0][e % VEC] = b[e];
+          }
+        } else {
+          gain[EARLY ? it : 0][0] = weight[g];
+          shift[EARLY ? it : 0][0] = bias != nullptr ? bias[g] : 0.f;
+        }
+      }
+    }
+  }
   wait_for_previous();
   const int out_row = blockIdx.x;
   const int row = rows != nullptr ? rows[out_row] : out_row;
   float* x = resid + static_cast<size_t>(row) * width;
   TO* y = out != nullptr ? out + static_cast<size_t>(out_row) * width : nullptr;
-  const int groups = width / VEC;
   if (rows == nullptr && branch == nullptr) {
     if (y != nullptr)
       for (int g = threadIdx.x; g < groups; g += blockDim.x) {
@@ -78,10 +104,10 @@ norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int p
     return;
   }
   const TD* d = branch != nullptr ? branch + static_cast<size_t>(row) * width : nullptr;
-  float held[MAX_PER_THREAD][VEC];
+  float held[PT][VEC], before[EARLY ? PT : 1][VEC];
   float sum = 0.f;
 #pragma unroll
-  for (int it = 0; it < MAX_PER_THREAD; ++it) {
+  for (int it = 0; it < PT; ++it) {
     const int g = threadIdx.x + it * blockDim.x;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) held[it][e] = 0.f;
@@ -91,11 +117,18 @@ norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int p
         if (rows != nullptr) {
           load4<float>(x + g * 4, v);
         } else {
+          if (EARLY) {   // the residual's loads go out with the slices'
+            float r[4];
+            load4<float>(x + g * 4, r);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) before[EARLY ? it : 0][e % VEC] = r[e];
+          }
           load_sum4<TD>(d + g * 4, partial_stride, partials, v);   // the slices of a K-split product, in ascending order
         }
 #pragma unroll
         for (int e = 0; e < 4; ++e) held[it][e % VEC] = v[e];
       } else {
+        if (EARLY && rows == nullptr) before[EARLY ? it : 0][0] = x[g];
         held[it][0] = rows != nullptr ? x[g] : load_sum<TD>(d + g, partial_stride, partials);
       }
 #pragma unroll
@@ -106,7 +139,7 @@ norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int p
   if (layer_norm) mean = block_sum(sum, scratch) / static_cast<float>(width);
   float sum_sq = 0.f;
 #pragma unroll
-  for (int it = 0; it < MAX_PER_THREAD; ++it) {
+  for (int it = 0; it < PT; ++it) {
     const int g = threadIdx.x + it * blockDim.x;
     if (g < groups) {
 #pragma unroll
@@ -118,31 +151,44 @@ norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int p
   }
   const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / static_cast<float>(width) + eps);
 #pragma unroll
-  for (int it = 0; it < MAX_PER_THREAD; ++it) {
+  for (int it = 0; it < PT; ++it) {
     const int g = threadIdx.x + it * blockDim.x;
     if (g < groups) {
       if (VEC == 4) {
         float w[4], b[4] = {0.f, 0.f, 0.f, 0.f}, r[4];
-        load4<float>(weight + g * 4, w);
-        if (bias != nullptr) load4<float>(bias + g * 4, b);
+        if (EARLY) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            w[e] = gain[EARLY ? it : 0][e % VEC];
+            b[e] = shift[EARLY ? it : 0][e % VEC];
+          }
+        } else {
+          load4<float>(weight + g * 4, w);
+          if (bias != nullptr) load4<float>(bias + g * 4, b);
+        }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           r[e] = __fmul_rn(__fmul_rn(held[it][e % VEC], inv), w[e]);
           if (bias != nullptr) r[e] = __fadd_rn(r[e], b[e]);
         }
         if (rows == nullptr) {
-          float before[4];
-          load4<float>(x + g * 4, before);
+          float old[4];
+          if (EARLY) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) r[e] = __fadd_rn(before[e], r[e]);
+            for (int e = 0; e < 4; ++e) old[e] = before[EARLY ? it : 0][e % VEC];
+          } else {
+            load4<float>(x + g * 4, old);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) r[e] = __fadd_rn(old[e], r[e]);
           store4<float>(x + g * 4, r);
         }
         if (y != nullptr) store4<TO>(y + g * 4, r);
       } else {
-        float v = __fmul_rn(__fmul_rn(held[it][0], inv), weight[g]);
-        if (bias != nullptr) v = __fadd_rn(v, bias[g]);
+        float v = __fmul_rn(__fmul_rn(held[it][0], inv), EARLY ? gain[EARLY ? it : 0][0] : weight[g]);
+        if (bias != nullptr) v = __fadd_rn(v, EARLY ? shift[EARLY ? it : 0][0] : bias[g]);
         if (rows == nullptr) {
-          v = __fadd_rn(x[g], v);
+          v = __fadd_rn(EARLY ? before[EARLY ? it : 0][0] : x[g], v);
           x[g] = v;
         }
         if (y != nullptr) y[g] = from_float<TO>(v);
@@ -244,7 +290,8 @@ __global__ void qk_norm_store_kernel(const float* __restrict__ qk, int partials,
 }
 
 // ------------------------------------------------- queries, latent and gate of a fused projection
-// One block per token.  fused [P][n][q_width + rank + gates] float32 (rank or gates may be 0).
+// One block per token.  fused [P][n][row_width] float32, of which the first q_width + rank + gates columns
+// are used (rank or gates may be 0; a row may be padded to a width the matrix product likes).
 // q_out [n][q_width]; the latent, divided by its root mean square and scaled by `latent_weight`, goes to
 // latent_cache[slot][padded] (padding zeroed); gate_out [n][gates] float32 = sigmoid.
 template <typename T>
@@ -252,7 +299,7 @@ __global__ void latent_store_kernel(const float* __restrict__ fused, int partial
                                     const float* __restrict__ latent_weight, float eps, T* __restrict__ q_out,
                                     T* __restrict__ latent_cache, const int* __restrict__ slots,
                                     float* __restrict__ gate_out, int q_width, int rank, int padded, int gates,
-                                    long long num_slots, int vec) {
+                                    int row_width, long long num_slots, int vec) {
   extern __shared__ __align__(16) float row_shared[];   // the token's latent
   __shared__ float scratch[33];
   let_dependents_start();
@@ -263,7 +310,7 @@ __global__ void latent_store_kernel(const float* __restrict__ fused, int partial
     if (slot < 0 || slot >= num_slots) slot = -1;
   }
   wait_for_previous();
-  const float* row = fused + static_cast<size_t>(token) * (q_width + rank + gates);
+  const float* row = fused + static_cast<size_t>(token) * row_width;
   if (vec) {   // the queries are the wide part: 16-byte loads, every slice of a K-split product in flight together
     for (int g = threadIdx.x; g < q_width / 4; g += blockDim.x) {
       float v[4];
@@ -324,16 +371,25 @@ static int launch_norm_rows(float* resid, const void* branch, int partials, long
   const bool vec = width % 4 == 0 && addresses % 16 == 0 && (partials == 1 || partial_stride % 4 == 0);
   const int groups = vec ? width / 4 : width;
   // many rows (prompts): bandwidth counts, small blocks whose threads keep several groups in flight;
-  // few rows (decoding): latency counts, one group per thread where a block can hold the row that way
-  int threads = ((groups + (n > 256 ? 3 : 0)) / (n > 256 ? 4 : 1) + 31) / 32 * 32;
+  // few rows (decoding): latency counts, one group per thread (two for rows beyond 1024 groups)
+  const bool few = n <= 256 && groups <= 2048;
+  const bool two = few && groups > 1024;
+  int threads = few ? ((two ? (groups + 1) / 2 : groups) + 31) / 32 * 32 : ((groups + 3) / 4 + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   if (static_cast<long long>(threads) * MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
-  if (vec)
-    launch_dependent(norm_rows_kernel<TD, TO, 4>, n, threads, 0, stream, resid, static_cast<const TD*>(branch), partials,
-                     partial_stride, rows, weight, bias, eps, layer_norm, static_cast<TO*>(out), width);
-  else
-    launch_dependent(norm_rows_kernel<TD, TO, 1>, n, threads, 0, stream, resid, static_cast<const TD*>(branch), partials,
-                     partial_stride, rows, weight, bias, eps, layer_norm, static_cast<TO*>(out), width);
+#define SHRIKE_NORM_ROWS_LAUNCH(V, P)                                                                              \
+  launch_dependent(norm_rows_kernel<TD, TO, V, P>, n, threads, 0, stream, resid, static_cast<const TD*>(branch), partials, \
+                   partial_stride, rows, weight, bias, eps, layer_norm, static_cast<TO*>(out), width)
+  if (vec) {
+    if (two) SHRIKE_NORM_ROWS_LAUNCH(4, 2);
+    else if (few) SHRIKE_NORM_ROWS_LAUNCH(4, 1);
+    else SHRIKE_NORM_ROWS_LAUNCH(4, MAX_PER_THREAD);
+  } else {
+    if (two) SHRIKE_NORM_ROWS_LAUNCH(1, 2);
+    else if (few) SHRIKE_NORM_ROWS_LAUNCH(1, 1);
+    else SHRIKE_NORM_ROWS_LAUNCH(1, MAX_PER_THREAD);
+  }
+#undef SHRIKE_NORM_ROWS_LAUNCH
   return SHRIKE_OK;
 }
 
@@ -405,21 +461,22 @@ SHRIKE_API int shrike_qk_norm_store(const float* qk, int partials, long long par
 
 SHRIKE_API int shrike_latent_store(const float* fused, int partials, long long partial_stride, const float* latent_weight,
                                    float eps, void* q_out, void* latent_cache, const int* slots, float* gate_out,
-                                   int dtype, int n, int q_width, int rank, int padded, int gates, long long num_slots,
-                                   cudaStream_t stream) {
+                                   int dtype, int n, int q_width, int rank, int padded, int gates, int row_width,
+                                   long long num_slots, cudaStream_t stream) {
   using namespace branch;
   if (n <= 0) return SHRIKE_OK;
-  if (partials < 1 || q_width <= 0 || rank < 0 || gates < 0 || padded < rank) return SHRIKE_BAD_ARGUMENT;
+  if (partials < 1 || q_width <= 0 || rank < 0 || gates < 0 || padded < rank || row_width < q_width + rank + gates)
+    return SHRIKE_BAD_ARGUMENT;
   if (rank > 0 && (latent_weight == nullptr || latent_cache == nullptr)) return SHRIKE_BAD_ARGUMENT;
   if (gates > 0 && gate_out == nullptr) return SHRIKE_BAD_ARGUMENT;
   const size_t smem = sizeof(float) * static_cast<size_t>(rank);
   if (smem > 48 * 1024) return SHRIKE_BAD_ARGUMENT;
-  const int vec = q_width % 4 == 0 && (q_width + rank + gates) % 4 == 0 && (partials == 1 || partial_stride % 4 == 0) &&
+  const int vec = q_width % 4 == 0 && row_width % 4 == 0 && (partials == 1 || partial_stride % 4 == 0) &&
                   (reinterpret_cast<uintptr_t>(fused) | reinterpret_cast<uintptr_t>(q_out)) % 16 == 0;
 #define SHRIKE_LATENT_CASE(T)                                                                                  \
   launch_dependent(latent_store_kernel<T>, n, 256, smem, stream, fused, partials, partial_stride, latent_weight, \
                    eps, static_cast<T*>(q_out), static_cast<T*>(latent_cache), slots, gate_out, q_width, rank,  \
-                   padded, gates, num_slots, vec)
+                   padded, gates, row_width, num_slots, vec)
   if (dtype == SHRIKE_F32) SHRIKE_LATENT_CASE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_LATENT_CASE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;

@@ -140,7 +140,13 @@ def core_library() -> ctypes.CDLL:
     return load_library("shrike_core", CORE_SOURCES)
 
 
+TENSOR_CORE_HEAD_DIM = 256   # the widest head the mma.sync and tcgen05 attention kernels are built for
+
+
 def attention_library(head_dim: int) -> ctypes.CDLL:
+    """The attention kernels for one head size; above `TENSOR_CORE_HEAD_DIM` the CUDA-core kernel alone."""
+    if head_dim > TENSOR_CORE_HEAD_DIM:
+        return load_library(f"shrike_attention_wide_d{head_dim}", ["attention_generic.cu"], {"SHRIKE_HEAD_DIM": head_dim})
     return load_library(f"shrike_attention_d{head_dim}", ATTENTION_SOURCES, {"SHRIKE_HEAD_DIM": head_dim})
 
 

@@ -130,7 +130,7 @@ class CudaOps:
         lib.shrike_act_mul.argtypes = [_P, _P, _I, _I, _I, _I, _I, _P]
         lib.shrike_norm_rows.argtypes = [_P, _P, _I, _I, _LL, _P, _P, _P, _F, _I, _P, _I, _I, _I, _P]
         lib.shrike_qk_norm_store.argtypes = [_P, _I, _LL, _P, _P, _F, _P, _F, _I, _P, _P, _P, _P] + [_I] * 6 + [_LL, _P]
-        lib.shrike_latent_store.argtypes = [_P, _I, _LL, _P, _F, _P, _P, _P, _P] + [_I] * 6 + [_LL, _P]
+        lib.shrike_latent_store.argtypes = [_P, _I, _LL, _P, _F, _P, _P, _P, _P] + [_I] * 7 + [_LL, _P]
         lib.shrike_head_scale.argtypes = [_P, _P, _I, _I, _I, _I, _P]
         lib.shrike_sample_slices.argtypes = [_I]
         lib.shrike_sample_slices.restype = _I
@@ -148,33 +148,38 @@ class CudaOps:
                 [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _F, _P, _P, _P]
             )
             lib.shrike_paged_attention_generic.restype = _I
-            lib.shrike_paged_attention_bf16.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _P]
-            )
-            lib.shrike_paged_attention_bf16.restype = _I
-            lib.shrike_paged_attention_bf16_scores.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _F, _P, _P]
-            )
-            lib.shrike_paged_attention_bf16_scores.restype = _I
-            lib.shrike_attention_single_token_pages.argtypes = [_I]
-            lib.shrike_attention_single_token_pages.restype = None
-            lib.shrike_attention_bf16_resident_ctas.restype = _I
-            lib.shrike_attention_tc_available.restype = _I
-            lib.shrike_paged_attention_tc_portions.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _P]
-            )
-            lib.shrike_paged_attention_tc_portions.restype = _I
-            lib.shrike_paged_attention_tc_portions_scores.argtypes = (
-                [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P]
-            )
-            lib.shrike_paged_attention_tc_portions_scores.restype = _I
-            lib.shrike_attention_tc_portions_rows.restype = _I
-            lib.shrike_attention_tc_portions_splits.argtypes = [_I, _I, _I, _I, _I]
-            lib.shrike_attention_tc_portions_splits.restype = _I
-            lib.shrike_attention_tc_portions_scratch_floats.argtypes = [_I, _I, _I]
-            lib.shrike_attention_tc_portions_scratch_floats.restype = _LL
+            if head_dim <= build.TENSOR_CORE_HEAD_DIM:
+                self._declare_tensor_core_attention(lib)
             self._attention[head_dim] = lib
         return lib
+
+    @staticmethod
+    def _declare_tensor_core_attention(lib):
+        lib.shrike_paged_attention_bf16.argtypes = (
+            [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _P]
+        )
+        lib.shrike_paged_attention_bf16.restype = _I
+        lib.shrike_paged_attention_bf16_scores.argtypes = (
+            [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _F, _P, _P]
+        )
+        lib.shrike_paged_attention_bf16_scores.restype = _I
+        lib.shrike_attention_single_token_pages.argtypes = [_I]
+        lib.shrike_attention_single_token_pages.restype = None
+        lib.shrike_attention_bf16_resident_ctas.restype = _I
+        lib.shrike_attention_tc_available.restype = _I
+        lib.shrike_paged_attention_tc_portions.argtypes = (
+            [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _P]
+        )
+        lib.shrike_paged_attention_tc_portions.restype = _I
+        lib.shrike_paged_attention_tc_portions_scores.argtypes = (
+            [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P]
+        )
+        lib.shrike_paged_attention_tc_portions_scores.restype = _I
+        lib.shrike_attention_tc_portions_rows.restype = _I
+        lib.shrike_attention_tc_portions_splits.argtypes = [_I, _I, _I, _I, _I]
+        lib.shrike_attention_tc_portions_splits.restype = _I
+        lib.shrike_attention_tc_portions_scratch_floats.argtypes = [_I, _I, _I]
+        lib.shrike_attention_tc_portions_scratch_floats.restype = _LL
 
     def _stream(self):
         return self._held_stream if self._held_stream is not None else torch.cuda.current_stream().cuda_stream
@@ -186,9 +191,10 @@ class CudaOps:
         self._held_stream = torch.cuda.current_stream().cuda_stream if hold else None
 
     def check_head_dim(self, head_dim: int):
-        if head_dim % 16 or not 16 <= head_dim <= 256:
+        if head_dim % 16 or not 16 <= head_dim <= 1024:
             raise KernelError(
-                f"head size {head_dim} is not served: the attention kernels take multiples of 16 from 16 to 256"
+                f"head size {head_dim} is not served: the attention kernels take multiples of 16 from 16 to 1024 "
+                "(the tensor-core ones up to 256)"
             )
 
     def layer_program(self):
@@ -297,8 +303,8 @@ class CudaOps:
             num_slots, self._stream()), "qk_norm_store")
 
     def latent_store(self, fused, latent_weight, eps, q_out, latents, slots, gate_out, q_width, rank, padded, gates):
-        """Splits a fused q|latent|gate projection ([N, q_width + rank + gates] float32 or a K-split
-        stack): queries cast to `q_out`, the latent divided by its root mean square and scaled by
+        """Splits a fused q|latent|gate projection ([N, at least q_width + rank + gates] float32 or a K-split
+        stack; further columns are padding): queries cast to `q_out`, the latent divided by its root mean square and scaled by
         `latent_weight` into the latent pages (`padded` elements a token), sigmoid of the gate columns
         to `gate_out` (float32).  rank 0: no latent of its own; gates 0: no gate."""
         _dense(fused, torch.float32, "fused projection")
@@ -311,7 +317,8 @@ class CudaOps:
         self.launches += 1
         _check(self.core.shrike_latent_store(
             _ptr(fused), partials, stride, _ptr(latent_weight), eps, _ptr(q_out), _ptr(latents), _ptr(slots),
-            _ptr(gate_out), self.code, fused.shape[-2], q_width, rank, padded, gates, num_slots, self._stream()),
+            _ptr(gate_out), self.code, fused.shape[-2], q_width, rank, padded, gates, fused.shape[-1], num_slots,
+            self._stream()),
             "latent_store")
 
     def head_scale(self, x, gate, heads, dim):
@@ -465,7 +472,7 @@ class CudaOps:
         lib = self._attention_lib(head_dim)
         num_seqs, max_blocks = block_table.shape
         page_size, num_pages = keys.shape[1], keys.shape[0]
-        if self.dtype == torch.float32:
+        if self.dtype == torch.float32 or head_dim > build.TENSOR_CORE_HEAD_DIM:
             self.launches += 1
             _check(lib.shrike_paged_attention_generic(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start),

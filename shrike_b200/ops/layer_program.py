@@ -105,7 +105,7 @@ class LayerProgram:
             return False
         if mixer.position is not None and mixer.position.rotary_table() is None:
             return False
-        if mixer.b_o is not None or feed_forward.spec.activation != "silu":
+        if mixer.b_o is not None or feed_forward.spec.activation != "silu" or mixer.spec.head_dim > build.TENSOR_CORE_HEAD_DIM:
             return False
         if not (mixer.spec.width % 8 == 0 and mixer.q_width % 8 == 0 and feed_forward.spec.intermediate % 8 == 0):
             return False

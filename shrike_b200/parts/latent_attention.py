@@ -74,6 +74,9 @@ class LatentAttention:
             self.latent_weight = tensors.pop("kv_norm.weight").to(torch.float32).contiguous()
         if spec.gated:
             rows.append(tensors.pop("gate.weight"))
+        used = sum(block.shape[0] for block in rows)
+        if used % 16:   # the library's fast product kernels want a row count they can tile: zero rows fill it up
+            rows.append(w_q.new_zeros(16 - used % 16, spec.width))
         self.w_in = torch.cat(rows).contiguous()
         self.q_width = heads * self.padded
         self.in_width = self.w_in.shape[0]

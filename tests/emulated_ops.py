@@ -22,7 +22,7 @@ class EmulatedOps:
         self.launches = 0
 
     def check_head_dim(self, head_dim):
-        if head_dim % 16 or not 16 <= head_dim <= 256:
+        if head_dim % 16 or not 16 <= head_dim <= 1024:
             raise ValueError(f"head size {head_dim} is not served")
 
     def embed(self, ids, table, out, previous=None, position_table=None, positions=None):
@@ -81,7 +81,7 @@ class EmulatedOps:
         n = fused.shape[0]
         q_out.copy_(fused[:, :q_width].to(q_out.dtype))
         if gates:
-            gate_out.copy_(torch.sigmoid(fused[:, q_width + rank:].float()))
+            gate_out.copy_(torch.sigmoid(fused[:, q_width + rank: q_width + rank + gates].float()))
         if rank and latents is not None:
             c = fused[:, q_width: q_width + rank].float()
             c = c / torch.sqrt(c.pow(2).mean(-1, keepdim=True) + eps) * latent_weight

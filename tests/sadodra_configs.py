@@ -68,8 +68,14 @@ SADODRA_LATENT_ONLY = {
     "layers": [_latent(3, 16, 8, 24, 0.4, ff=40)],
 }
 
-SADODRA = {"A": SADODRA_A, "B": SADODRA_B, "attention": SADODRA_ATTENTION_ONLY, "latent": SADODRA_LATENT_ONLY}
-SADODRA_SEEDS = {"A": 11, "B": 12, "attention": 13, "latent": 14}
+# a latent wider than the tensor-core attention kernels' heads (300 -> 304 > 256): the CUDA-core kernel serves it
+SADODRA_WIDE_LATENT = {
+    "architecture": "Sadodra", "width": 64, "vocab": 89, "max_positions": 300, "norm": {"eps": 1e-5},
+    "layers": [_latent(2, 16, 16, 300, 0.3, ff=48), _attention(2, 1, 16, 0.3, window=11, ff=32), _latent(3, 8, 8, 300, 0.3, kv_from=0)],
+}
+
+SADODRA = {"wide": SADODRA_WIDE_LATENT, "A": SADODRA_A, "B": SADODRA_B, "attention": SADODRA_ATTENTION_ONLY, "latent": SADODRA_LATENT_ONLY}
+SADODRA_SEEDS = {"wide": 15, "A": 11, "B": 12, "attention": 13, "latent": 14}
 
 
 def sharpened(tensors: dict) -> dict:

@@ -567,7 +567,7 @@ def test_head_sizes_outside_the_served_range_are_refused():
     from shrike_b200.ops.cuda_ops import KernelError
 
     ops = cuda_ops(torch.float32)
-    for bad in (8, 24, 272, 100):
+    for bad in (8, 24, 1040, 100):
         with pytest.raises(KernelError, match="head size"):
             ops.check_head_dim(bad)
 

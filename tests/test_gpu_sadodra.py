@@ -20,7 +20,7 @@ from tests.plain import plain_sadodra as ps
 from tests.sadodra_configs import SADODRA, make_sadodra_folder
 
 pytestmark = pytest.mark.gpu
-LENGTHS = {"A": [5, 47, 1, 130, 2, 64, 33], "B": [5, 17, 150, 70, 1, 90, 2], "attention": [40, 3, 25], "latent": [40, 3, 25]}
+LENGTHS = {"wide": [30, 2, 45], "A": [5, 47, 1, 130, 2, 64, 33], "B": [5, 17, 150, 70, 1, 90, 2], "attention": [40, 3, 25], "latent": [40, 3, 25]}
 _cache = {}
 
 
@@ -95,7 +95,7 @@ WAYS = {
 
 @pytest.mark.parametrize("way", list(WAYS))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key,page", [("A", 16), ("B", 16), ("A", 8), ("B", 24), ("attention", 4), ("latent", 32)])
+@pytest.mark.parametrize("key,page", [("A", 16), ("B", 16), ("A", 8), ("B", 24), ("attention", 4), ("latent", 32), ("wide", 16)])
 def test_replay_matches_plain(tmp_path_factory, key, page, dtype, way):
     folder, requests, want, scale, limits = reference(key, dtype, tmp_path_factory)
     steps = WAYS[way](requests)
@@ -235,3 +235,26 @@ def test_trace_run_program_serves_the_design(tmp_path):
     check(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, 211), ref_a[[0, 29]], scale, limit_a, "step 0")
     check(np.fromfile(out / "1.f32", dtype="<f4").reshape(1, 211), ref_b[[8]], scale, limit_b, "step 1")
     check(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, 211), ref_a[[40]], scale, limit_a, "step 2")
+
+
+def test_command_line_programs_serve_the_design(tmp_path):
+    """The interactive program from a shape without a folder, and the one-prompt program on a folder."""
+    import os
+
+    bin_dir = Path(__file__).resolve().parents[1] / "bin"
+
+    def run(program, arguments, text=""):
+        done = subprocess.run([sys.executable, str(bin_dir / program), *arguments], input=text, capture_output=True,
+                              text=True, timeout=900, env=dict(os.environ, PYTHONUNBUFFERED="1"))
+        assert done.returncode == 0, done.stderr[-3000:]
+        return done
+
+    done = run("shrike_b200", ["--random", "sadodra-tiny", "--seed", "1", "--num-blocks", "32"], "/temp 0\n/max 4\n1 2 3\n/exit\n")
+    assert "shape sadodra-tiny" in done.stdout and "[4 tok |" in done.stdout
+    folder = make_sadodra_folder(tmp_path, "A")
+    prompt = [7, 200, 41, 41, 2]
+    want, margins = ps.greedy_continue(SADODRA["A"], read_weights(folder), prompt, 6)
+    assert min(margins) > 1e-4
+    done = run("shrike_b200_complete", [" ".join(map(str, prompt)), "--model", str(folder), "--max-tokens", "6",
+                                         "--dtype", "float32", "--num-blocks", "8", "--block-size", "8"])
+    assert [int(t) for t in done.stdout.split()] == want

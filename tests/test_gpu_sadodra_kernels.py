@@ -117,7 +117,7 @@ def test_gelu_gate_in_the_product_epilogue_equals_the_separate_kernel(tokens, in
 # ------------------------------------------------------------------ queries and keys
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,temperature,partials", [(4, 2, 32, (0.3, 16), 1), (3, 3, 24, (0.7, 5), 3),
-                                                                     (5, 1, 64, None, 2), (2, 2, 16, (0.25, 1), 1)])
+                                                                     (5, 1, 64, None, 2), (2, 2, 16, (0.25, 1), 1), (3, 1, 10, (0.5, 3), 2)])
 def test_queries_and_keys_are_normed_over_the_whole_projection(dtype, heads, kv_heads, dim, temperature, partials):
     ops = cuda_ops(dtype)
     padded = -(-dim // 16) * 16
