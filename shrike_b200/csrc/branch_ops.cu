@@ -23,15 +23,20 @@ template <typename T> __device__ __forceinline__ void load_sum4(const T* base, l
 template <> __device__ __forceinline__ void load_sum4<float>(const float* base, long long stride, int partials, float (&v)[4]) {
   sum_partials4(base, stride, partials, v);
 }
-template <> __device__ __forceinline__ void load_sum4<__nv_bfloat16>(const __nv_bfloat16* base, long long stride, int partials,
-                                                                     float (&v)[4]) {
-  load4<__nv_bfloat16>(base, v);
+// slice after slice: few registers, for the forms that run many rows (which a K-split product never feeds)
+template <typename T>
+__device__ __forceinline__ void load_sum4_in_turn(const T* base, long long stride, int partials, float (&v)[4]) {
+  load4<T>(base, v);
   for (int p = 1; p < partials; ++p) {
     float more[4];
-    load4<__nv_bfloat16>(base + p * stride, more);
+    load4<T>(base + p * stride, more);
 #pragma unroll
     for (int e = 0; e < 4; ++e) v[e] = __fadd_rn(v[e], more[e]);
   }
+}
+template <> __device__ __forceinline__ void load_sum4<__nv_bfloat16>(const __nv_bfloat16* base, long long stride, int partials,
+                                                                     float (&v)[4]) {
+  load_sum4_in_turn<__nv_bfloat16>(base, stride, partials, v);
 }
 
 template <typename T> __device__ __forceinline__ float load_sum(const T* base, long long stride, int partials);
@@ -53,9 +58,12 @@ template <> __device__ __forceinline__ float load_sum<__nv_bfloat16>(const __nv_
 // v / sqrt(mean(v^2) + eps) * w (+ b).
 // PT: groups a thread may hold.  PT <= 2 (few rows, decoding: latency counts) reads the norm's weight and bias
 // before the wait (no kernel writes them) and has the residual and the branch's slices in flight together, so
-// that the row costs one memory round trip; PT = 8 (many rows: bandwidth counts) reads them where it needs them.
+// that the row costs one memory round trip; PT = 4 or 8 (many rows: bandwidth counts) reads them where it needs
+// them.  PT = 4 (rows of up to 1,024 groups) is built for five blocks of up to 256 threads an SM: with the 64
+// registers a block of 1,024 threads may take, four blocks of 224 threads fit and the loads of 41 % of the
+// SM's warps are all that is in flight (measured: 3.5 TB/s at rows of 3,584).
 template <typename TD, typename TO, int VEC, int PT>
-__global__ void __launch_bounds__(1024, 1)
+__global__ void __launch_bounds__(PT == 4 ? 256 : 1024, PT == 4 ? 5 : 1)
 norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int partials, long long partial_stride,
                  const int* __restrict__ rows, const float* __restrict__ weight, const float* __restrict__ bias,
                  float eps, int layer_norm, TO* __restrict__ out, int width) {
@@ -123,7 +131,9 @@ norm_rows_kernel(float* __restrict__ resid, const TD* __restrict__ branch, int p
 #pragma unroll
             for (int e = 0; e < 4; ++e) before[EARLY ? it : 0][e % VEC] = r[e];
           }
-          load_sum4<TD>(d + g * 4, partial_stride, partials, v);   // the slices of a K-split product, in ascending order
+          // the slices of a K-split product, in ascending order
+          if (EARLY) load_sum4<TD>(d + g * 4, partial_stride, partials, v);
+          else load_sum4_in_turn<TD>(d + g * 4, partial_stride, partials, v);
         }
 #pragma unroll
         for (int e = 0; e < 4; ++e) held[it][e % VEC] = v[e];
@@ -377,16 +387,19 @@ static int launch_norm_rows(float* resid, const void* branch, int partials, long
   int threads = few ? ((two ? (groups + 1) / 2 : groups) + 31) / 32 * 32 : ((groups + 3) / 4 + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   if (static_cast<long long>(threads) * MAX_PER_THREAD < groups) return SHRIKE_BAD_ARGUMENT;
+  const bool four = !few && threads <= 256;   // rows of up to 1,024 groups: four groups a thread
 #define SHRIKE_NORM_ROWS_LAUNCH(V, P)                                                                              \
   launch_dependent(norm_rows_kernel<TD, TO, V, P>, n, threads, 0, stream, resid, static_cast<const TD*>(branch), partials, \
                    partial_stride, rows, weight, bias, eps, layer_norm, static_cast<TO*>(out), width)
   if (vec) {
     if (two) SHRIKE_NORM_ROWS_LAUNCH(4, 2);
     else if (few) SHRIKE_NORM_ROWS_LAUNCH(4, 1);
+    else if (four) SHRIKE_NORM_ROWS_LAUNCH(4, 4);
     else SHRIKE_NORM_ROWS_LAUNCH(4, MAX_PER_THREAD);
   } else {
     if (two) SHRIKE_NORM_ROWS_LAUNCH(1, 2);
     else if (few) SHRIKE_NORM_ROWS_LAUNCH(1, 1);
+    else if (four) SHRIKE_NORM_ROWS_LAUNCH(1, 4);
     else SHRIKE_NORM_ROWS_LAUNCH(1, MAX_PER_THREAD);
   }
 #undef SHRIKE_NORM_ROWS_LAUNCH
