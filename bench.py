@@ -564,8 +564,11 @@ def run_case(args) -> dict:
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3)
         work = {"bytes": rows * h * (4 + 4 + 4 + 2)}
-    elif args.case in ("attention_single", "attention_portions", "attention_single_scores", "attention_portions_scores"):
+    elif args.case in ("attention_single", "attention_portions", "attention_single_scores", "attention_portions_scores",
+                       "attention_single_latent", "attention_portions_latent"):
         single = args.case.startswith("attention_single")
+        if args.case.endswith("_latent"):   # one key/value head of 256 whose keys are its values, as a cached latent is read
+            kv, d = 1, 256
         changed = args.case.endswith("_scores")   # a soft cap and a distance bias on every score
         softcap = 50.0 if changed else None
         slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / heads) for i in range(heads)], device=dev) if changed else None
@@ -575,7 +578,7 @@ def run_case(args) -> dict:
         blocks = -(-ctx_len // BLOCK_SIZE)
         pages = seqs * blocks + 8
         keys = torch.randn(pages, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16)
-        values = torch.randn_like(keys)
+        values = keys if args.case.endswith("_latent") else torch.randn_like(keys)
         q = torch.randn(seqs * q_len, heads * d, device=dev, dtype=torch.bfloat16)
         width = max(8, 1 << (blocks - 1).bit_length())
         table = torch.full((seqs, width), -1, dtype=torch.int32, device=dev)
@@ -592,7 +595,8 @@ def run_case(args) -> dict:
             stop.record()
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3)
-        work = {"bytes": seqs * ctx_len * 2 * kv * d * 2} if single else {"flops": 4.0 * heads * d * q_len * (q_len + 1) / 2}
+        planes = 1 if args.case.endswith("_latent") else 2
+        work = {"bytes": seqs * ctx_len * planes * kv * d * 2} if single else {"flops": 4.0 * heads * d * q_len * (q_len + 1) / 2}
     else:
         raise SystemExit(f"unknown case {args.case!r}")
     ops.check_status()
@@ -867,7 +871,8 @@ def main():
                         help="--case design: the widths at which the Sadodra decoder and the Qwen2 decoder are compared")
     parser.add_argument("--case", default=None,
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
-                             "gemm_qkv, attention_single, attention_portions (with _scores: soft-capped and distance-biased), "
+                             "gemm_qkv, attention_single, attention_portions (with _scores: soft-capped and distance-biased; with _latent: "
+                             "one key/value head of 256 whose keys are its values), "
                              "branch_norm; --batch gives tokens / sequences / rows.  timeline: per-kernel "
                              "times inside one captured decode step (--layers, default 6).  design: the Sadodra decoder "
                              "beside the Qwen2 decoder of equal widths (--design), prefill and decode")

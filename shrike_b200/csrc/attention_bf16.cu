@@ -147,7 +147,8 @@ __device__ __forceinline__ void locate_tile(long long* rows, const Params& p, co
 // consecutive 16-byte chunks of a row, so a warp's copies cover whole 128-byte lines.
 // Keys without a row become zeros.
 template <int KEYS, int NTHREADS>
-__device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Params& p, const long long* rows) {
+__device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Params& p, const long long* rows,
+                                          bool with_values = true) {
   constexpr int ROUNDS = (KEYS * CHUNKS + NTHREADS - 1) / NTHREADS;
   long long row[ROUNDS];
 #pragma unroll
@@ -163,17 +164,18 @@ __device__ __forceinline__ void copy_tile(bf16* k_tile, bf16* v_tile, const Para
     const bool valid = row[i] >= 0;
     const size_t offset = valid ? static_cast<size_t>(row[i]) + chunk * 8 : 0;
     cp_async16(k_tile + key * ROW + chunk * 8, p.k_cache + offset, valid);
-    cp_async16(v_tile + key * ROW + chunk * 8, p.v_cache + offset, valid);
+    if (with_values) cp_async16(v_tile + key * ROW + chunk * 8, p.v_cache + offset, valid);
   }
 }
 
 // Both steps at once, with a barrier between them (for code that loads one tile ahead).
 template <int KEYS>
 __device__ __forceinline__ void load_kv_tile(bf16* k_tile, bf16* v_tile, long long* rows, const Params& p,
-                                             const int* table, int kv_head, int tile_base, int lo, int hi) {
+                                             const int* table, int kv_head, int tile_base, int lo, int hi,
+                                             bool with_values = true) {
   locate_tile<KEYS>(rows, p, table, kv_head, tile_base, lo, hi);
   __syncthreads();
-  copy_tile<KEYS, THREADS>(k_tile, v_tile, p, rows);
+  copy_tile<KEYS, THREADS>(k_tile, v_tile, p, rows, with_values);
 }
 
 // S[16 x (8 * NT)] += Q[16 x D] * K^T for keys [key0, key0 + 8 * NT) of the tile.
@@ -298,7 +300,9 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
     const bf16* src = p.q + (static_cast<size_t>(start + tile_start + (valid ? row : 0)) * p.num_heads + head) * D + chunk * 8;
     cp_async16(q_tile + row * ROW + chunk * 8, src, valid);
   }
-  load_kv_tile<PBN>(k_tiles, v_tiles, tile_rows[0], p, table, kv_head, tile_lo * PBN, lo, hi);
+  // keys that are their own values (a cached latent, one plane of pages): one tile serves both products
+  const bool own_values = p.k_cache != p.v_cache;
+  load_kv_tile<PBN>(k_tiles, v_tiles, tile_rows[0], p, table, kv_head, tile_lo * PBN, lo, hi, own_values);
   cp_async_commit();
 
   int first[2], last[2];
@@ -323,7 +327,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
     const int buffer = (tile - tile_lo) & 1;
     if (tile < tile_hi) {
       load_kv_tile<PBN>(k_tiles + (buffer ^ 1) * PBN * ROW, v_tiles + (buffer ^ 1) * PBN * ROW, tile_rows[buffer ^ 1], p,
-                        table, kv_head, (tile + 1) * PBN, lo, hi);
+                        table, kv_head, (tile + 1) * PBN, lo, hi, own_values);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
       const bf16* k_tile = k_tiles + buffer * PBN * ROW;
-      const bf16* v_tile = v_tiles + buffer * PBN * ROW;
+      const bf16* v_tile = own_values ? v_tiles + buffer * PBN * ROW : k_tile;
       scores<PBN / 8, false>(s, q_frag, q_rows, k_tile, 0, lane);
       softmax_update<PBN / 8>(s, o, row_max, row_sum, first, last, tile * PBN, p.scale_log2, lane, modified, p.scale, p.softcap, slope);
       accumulate<PBN / 8>(o, s, v_tile, 0, lane);
