@@ -475,9 +475,18 @@ def run_mixed(args) -> dict:
     from shrike_b200.weights.random_init import random_tensors
 
     torch.cuda.set_device(0)
-    raw = dict(MODEL_1_5B)
-    if args.layers:
-        raw["num_hidden_layers"] = args.layers
+    sadodra = getattr(args, "arch", "qwen2") == "sadodra"   # the same workload on the Sadodra decoder at the same widths
+    if sadodra:
+        from shrike_b200.shapes import shape_config
+
+        raw = dict(shape_config("sadodra-1.5b"))
+        if args.layers:
+            raw["layers"] = raw["layers"][: args.layers]
+        raw["vocab_size"], raw["num_hidden_layers"] = raw["vocab"], len(raw["layers"])
+    else:
+        raw = dict(MODEL_1_5B)
+        if args.layers:
+            raw["num_hidden_layers"] = args.layers
     config = parse_config(raw)
     tensors = random_tensors(config, seed=0, device="cuda", dtype=torch.bfloat16)
     engine = LLMEngine(None, block_size=BLOCK_SIZE, num_blocks=args.num_blocks or 12000, max_tokens_per_step=512,
@@ -498,7 +507,8 @@ def run_mixed(args) -> dict:
     generated = sum(len(r) for r in results)
     assert [len(r) for r in results] == outputs and engine.block_manager.whole()
     return {
-        "workload": "mixed", "model": "Qwen2.5-1.5B shape", "layers": raw["num_hidden_layers"], "requests": 64,
+        "workload": "mixed", "model": "Sadodra at Qwen2.5-1.5B widths" if sadodra else "Qwen2.5-1.5B shape",
+        "layers": raw["num_hidden_layers"], "requests": 64,
         "prompt_tokens": sum(len(p) for p in prompts), "generated_tokens": generated, "seconds": round(seconds, 3),
         "value": round(generated / seconds, 1), "unit": "generated tok/s",
         "total_tokens_per_second": round((generated + sum(len(p) for p in prompts)) / seconds, 1),
@@ -863,6 +873,8 @@ def main():
     parser.add_argument("--context", type=int, default=1024, help="tokens each sequence holds when decoding is timed")
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")
+    parser.add_argument("--arch", default="qwen2", choices=["qwen2", "sadodra"],
+                        help="--workload mixed: the decoder the 64 requests run on (both at Qwen2.5-1.5B widths)")
     parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")
     parser.add_argument("--skip-mixed", action="store_true", help="leave the mixed workload out of the default line")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
