@@ -47,6 +47,12 @@ def _ptr(tensor):
 _LIMITS = {
     "add_rmsnorm": "the row width must be at most 32768 (8192 when it is no multiple of 4)",
     "gather_add_rmsnorm": "the row width must be at most 32768 (8192 when it is no multiple of 4)",
+    "norm_add": "the row width must be at most 32768 (8192 when it is no multiple of 4)",
+    "gather_norm": "the row width must be at most 32768 (8192 when it is no multiple of 4)",
+    "qk_norm_store": "a token's queries and keys together must fit an SM's shared memory (about 58,000 elements)",
+    "latent_store": "the latent's rank must be at most 12288 and the row at least as wide as queries, latent and gates",
+    "head_scale": "the head size must be a multiple of 4 and the array 16-byte aligned",
+    "act_mul": "the activation must be one the kernels know and the run length divide the row",
     "gemm_tcgen05": "K must be a multiple of 8 and the operands 16-byte aligned",
     "paged_attention_bf16": "at most 65535 sequences and heads, heads a multiple of kv heads, at most 32 splits",
 }
