@@ -190,6 +190,30 @@ def test_captured_decode_steps_equal_eager_ones(tmp_path_factory, key, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_steps_with_portions_equal_eager_ones(tmp_path_factory, dtype):
+    """A batch shape with portions is recorded when it has come several times; ten requests fed in two equal
+    portions each make one shape come twenty times."""
+    from shrike_b200.replay import TraceSession
+
+    folder, _, _, _, _ = reference("A", dtype, tmp_path_factory)
+    steps = []
+    for index in range(10):
+        tokens = random_tokens(SADODRA["A"]["vocab"], 48, 900 + index)
+        for half in (0, 1):
+            steps.append({"step": len(steps), "entries": [{"id": f"p{index}", "tokens": tokens[24 * half: 24 * half + 24],
+                                                           "want": list(range(24))}], "end": [f"p{index}"] if half else []})
+    results = []
+    for graphs in (True, False):
+        session = TraceSession(folder, dtype, 256, page_size=16, max_live=4)
+        session.runner.use_graphs = graphs
+        results.append([session.step(record).copy() for record in steps])
+        if graphs:
+            assert any(not isinstance(key[0], int) for key in session.runner._graphs), "no step with a portion was captured"
+    for a, b in zip(*results):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("key,lengths,new", [("A", (5, 17, 33), 8), ("B", (3, 40, 75), 8)])
 def test_greedy_generation_through_the_engine(tmp_path_factory, key, lengths, new, dtype):
     from shrike_b200 import SamplingParams
