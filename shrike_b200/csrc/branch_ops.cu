@@ -450,7 +450,10 @@ SHRIKE_API int shrike_qk_norm_store(const float* qk, int partials, long long par
   const uintptr_t addresses = reinterpret_cast<uintptr_t>(qk) | reinterpret_cast<uintptr_t>(q_out) |
                               reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache);
   const bool vec = dim % 4 == 0 && padded % 4 == 0 && addresses % 16 == 0 && (partials == 1 || partial_stride % 4 == 0);
-  const int threads = n > 256 ? 128 : 256;
+  // few tokens (decoding): a thread a group, so that a token's loads are one round trip; many: small blocks
+  const int row_groups = (num_heads + num_kv_heads) * dim / (vec ? 4 : 1);
+  int threads = n > 256 ? 128 : 256;
+  if (n <= 64) threads = row_groups >= 1024 ? 1024 : (row_groups + 31) / 32 * 32 < 128 ? 128 : (row_groups + 31) / 32 * 32;
 #define SHRIKE_QK_LAUNCH(T, V)                                                                               \
   do {                                                                                                       \
     if (smem > 48 * 1024) {                                                                                  \
