@@ -483,7 +483,7 @@ SHRIKE_API int shrike_latent_store(const float* fused, int partials, long long p
   if (n <= 0) return SHRIKE_OK;
   if (partials < 1 || q_width <= 0 || rank < 0 || gates < 0 || padded < rank || row_width < q_width + rank + gates)
     return SHRIKE_BAD_ARGUMENT;
-  if (rank > 0 && (latent_weight == nullptr || latent_cache == nullptr)) return SHRIKE_BAD_ARGUMENT;
+  if (rank > 0 && latent_weight == nullptr) return SHRIKE_BAD_ARGUMENT;   // without pages the latent is only skipped over
   if (gates > 0 && gate_out == nullptr) return SHRIKE_BAD_ARGUMENT;
   const size_t smem = sizeof(float) * static_cast<size_t>(rank);
   if (smem > 48 * 1024) return SHRIKE_BAD_ARGUMENT;
