@@ -1,7 +1,7 @@
 """Cache manager: page ids, block tables and state slots.  Owns no device memory.
 
 Pages.  Keys and values live in pages of `page_size` tokens.  Caches with the same
-needs (kv heads, head size, window) form a group; every group has a pool of pages
+needs (kv heads, head size, window or chunk) form a group; every group has a pool of pages
 of its own and every request one block table per group.  Logical block i of a
 request covers positions [i * page_size, (i + 1) * page_size).
 
@@ -38,6 +38,21 @@ class KVGroupSpec:
     head_dim: int
     window: int | None = None
     planes: int = 2   # tensors a token holds in a page: keys and values, or one that serves as both
+    # positions cut into runs of `chunk`, counted from 0: a query sees the keys of its own run only
+    chunk: int | None = None
+
+    @property
+    def span(self) -> int | None:
+        """The most keys before and including a query that it can see (None: all of them)."""
+        return self.window if self.window is not None else self.chunk
+
+    def first_needed(self, position: int) -> int:
+        """The first key a query at `position` (and so any later one) still sees."""
+        if self.window is not None:
+            return position - self.window + 1
+        if self.chunk is not None:
+            return position // self.chunk * self.chunk
+        return 0
 
 
 class IdPool:
@@ -120,7 +135,7 @@ class CacheManager:
             raise ValueError("one page count per group")
         self.pools = [IdPool(count) for count in counts]
         self.slots = IdPool(max_slots)
-        self.has_windows = any(group.window is not None for group in self.groups)
+        self.has_windows = any(group.span is not None for group in self.groups)
         self._opened: list[int] = []   # slots handed out since `take_opened` was last called
 
     # ---- figures -----------------------------------------------------------
@@ -148,8 +163,8 @@ class CacheManager:
     def portion_limit(self) -> int | None:
         """The longest portion one request can be fed in a step, whatever else is free: a group
         with a window must hold the window and the portion at once (None: no such bound)."""
-        limits = [max(1, (pool.count - 2) * self.page_size - group.window + 2)
-                  for pool, group in zip(self.pools, self.groups) if group.window is not None]
+        limits = [max(1, (pool.count - 2) * self.page_size - group.span + 2)
+                  for pool, group in zip(self.pools, self.groups) if group.span is not None]
         return min(limits) if limits else None
 
     def whole(self) -> bool:
@@ -163,7 +178,7 @@ class CacheManager:
         """Pages per group a request of `tokens` may hold at once when it is fed at most `portion`
         tokens a step (None: all at once).  A group with a window holds the pages that the
         window and the portion in flight touch, whatever the request's length."""
-        return [pages_in_flight(self.blocks_for(tokens), group.window, min(portion or tokens, tokens), self.page_size)
+        return [pages_in_flight(self.blocks_for(tokens), group.span, min(portion or tokens, tokens), self.page_size)
                 for group in self.groups]
 
     # ---- a request's life ----------------------------------------------------
@@ -214,14 +229,15 @@ class CacheManager:
     def advance(self, cache: RequestCache, num_computed: int) -> int:
         """After a step: gives back the pages that every later query's window has
         passed.  The next query sits at position `num_computed` and sees keys from
-        `num_computed - window + 1` on.  Returns how many pages were given back."""
+        `num_computed - window + 1` on (with chunks: from the start of its own run of positions).
+        Returns how many pages were given back."""
         if not self.has_windows:
             return 0
         given = 0
         for table, pool, group in zip(cache.tables, self.pools, self.groups):
-            if group.window is None:
+            if group.span is None:
                 continue
-            first_needed = num_computed - group.window + 1
+            first_needed = group.first_needed(num_computed)
             passed = min(max(0, first_needed // self.page_size), table.length)
             for index in range(table.released, passed):
                 pool.give_back(int(table.pages[index]))
@@ -246,7 +262,8 @@ class CacheManager:
 
 
 def pages_in_flight(whole: int, window: int | None, portion: int, page_size: int) -> int:
-    """Pages one request holds at most in a group: all `whole` of them, or, with a window, those
+    """Pages one request holds at most in a group: all `whole` of them, or, with a window (or chunks of
+    that many positions, whose queries never see further back than a window of the chunk's size), those
     from the first key the portion's first query still sees to the portion's last token."""
     if window is None:
         return whole
@@ -258,7 +275,7 @@ def pages_per_group(groups, page_size: int, budget_bytes: int, bytes_per_page: l
     """Page counts for a budget of bytes: every group without a window gets the same count N, a
     group with a window at most what `max_slots` requests fed `max_portion` tokens a step can
     hold of it; N is as large as the budget allows."""
-    caps = [None if group.window is None else max_slots * pages_in_flight(1 << 40, group.window, max_portion, page_size)
+    caps = [None if group.span is None else max_slots * pages_in_flight(1 << 40, group.span, max_portion, page_size)
             for group in groups]
     capped: set[int] = set()
     while True:
@@ -278,6 +295,6 @@ def group_caches(needs: dict[int, object]) -> list[KVGroupSpec]:
     groups: dict[tuple, list[int]] = {}
     for cache_id in sorted(needs):
         need = needs[cache_id]
-        key = (need.num_kv_heads, need.head_dim, need.window, getattr(need, "planes", 2))
+        key = (need.num_kv_heads, need.head_dim, need.window, getattr(need, "planes", 2), getattr(need, "chunk", None))
         groups.setdefault(key, []).append(cache_id)
     return [KVGroupSpec(tuple(ids), *key) for key, ids in groups.items()]

@@ -148,13 +148,133 @@ class LatentAttentionSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class DynamicTanhSpec(PartSpec):
+    """A norm without statistics: tanh(alpha x) * weight + bias, alpha one learned number."""
+
+    width: int
+    kind: str = field(init=False, default="dynamic_tanh")
+
+
+@dataclass(frozen=True)
+class GatedHeadAttentionSpec(PartSpec):
+    """Grouped-query softmax attention over a paged key/value cache with, each optional:
+
+    `qkv_bias` / `out_bias`; `qk_norm`: q and k divided by their root mean square PER HEAD and scaled
+    by one weight of the head's size that all heads share (before rotation); `rotary` (dims, base):
+    the first `dims` dimensions of each head rotate, dimension i with i + dims/2, by
+    position * base^(-2i/dims), the rest pass; `window`: a query sees the `window` latest keys;
+    `chunk`: a query at position p sees key j <= p only if floor(p / chunk) = floor(j / chunk), runs
+    counted from position 0 of the sequence; `head_gate`: head h's output times sigmoid(Wg x)_h.
+    Keys have `head_dim` elements, values `value_dim`.
+    """
+
+    width: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    qkv_bias: bool = False
+    out_bias: bool = False
+    qk_norm: bool = False
+    rotary: tuple | None = None
+    window: int | None = None
+    chunk: int | None = None
+    head_gate: bool = False
+    kind: str = field(init=False, default="gated_head_attention")
+
+    def __post_init__(self):
+        if self.num_heads % self.num_kv_heads:
+            raise ConfigError(f"heads={self.num_heads} is not a multiple of kv_heads={self.num_kv_heads}")
+        if self.window is not None and self.chunk is not None:
+            raise ConfigError("an attention layer has a window or a chunk, not both")
+        for name in ("window", "chunk"):
+            if getattr(self, name) is not None and getattr(self, name) < 1:
+                raise ConfigError(f"attention {name} must be >= 1, got {getattr(self, name)}")
+        if self.rotary is not None:
+            dims = self.rotary[0]
+            if isinstance(dims, bool) or not isinstance(dims, int) or dims < 2 or dims % 2 or dims > self.head_dim:
+                raise ConfigError(f"rotary dims must be even and at most the head size {self.head_dim}, got {dims!r}")
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec(PartSpec):
+    """A recurrent mixer whose state is a matrix per head (the mLSTM cell of xLSTM), with an
+    exponential input gate, a sigmoid forget gate (both soft-capped at `gate_cap` before their
+    nonlinearity) and a running maximum that keeps the exponentials in range:
+
+        m_t = max(f_t + m_(t-1), i_t);  S_t = exp(f_t + m_(t-1) - m_t) S_(t-1) + exp(i_t - m_t) k_t v_t^T
+        z_t likewise with k_t alone;  o_t = S_t^T q_t / (max(|z_t . q_t|, exp(-m_t)) + `denominator_floor`)
+
+    q is scaled by head_dim^(-1/2).  Each head's output is divided by its root mean square, the heads
+    are scaled by one weight, gated by sigmoid(Wg x) and projected.  `m_0` is the running maximum a
+    sequence starts with; state and gates are 32-bit.
+    """
+
+    width: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    gate_cap: float
+    eps: float
+    denominator_floor: float = 1e-6
+    initial_max: float = 0.0
+    kind: str = field(init=False, default="matrix_memory")
+
+    def __post_init__(self):
+        if not self.gate_cap > 0:
+            raise ConfigError(f"gate_cap must be positive, got {self.gate_cap}")
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec(PartSpec):
+    """Several mixers that read the same input; their outputs are added with a scale each.
+    `branches`: (name, spec, scale); a branch's tensors are named `<name>.<its own names>`."""
+
+    width: int
+    branches: tuple
+    kind: str = field(init=False, default="parallel_mixer")
+
+    def __post_init__(self):
+        if not self.branches:
+            raise ConfigError("a parallel mixer needs at least one branch")
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
     """Dense gated feed-forward: down(act(gate(x)) * up(x)) (shrike/models/qwen.py:128-136)."""
 
     width: int
     intermediate: int
     activation: str
+    # for the activation "clamped_swish": g <- min(g, limit), u <- clamp(u, -limit, limit), then
+    # g * sigmoid(1.702 g) * (u + 1)
+    limit: float | None = None
     kind: str = field(init=False, default="gated_mlp")
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec(PartSpec):
+    """A mixture of gated feed-forward experts: router logits in 32-bit, softmax over all experts,
+    the `top` largest, their scores divided by the sum of those (+ `renorm_eps`); the output is the
+    weighted sum of the chosen experts' down(act(gate x) * (up x)).  `shared_intermediate` (None: no
+    shared expert): one more expert of that size that every token uses, times sigmoid(w_sg . x)
+    when `shared_gate`."""
+
+    width: int
+    experts: int
+    top: int
+    intermediate: int
+    activation: str = "silu"
+    shared_intermediate: int | None = None
+    shared_gate: bool = True
+    renorm_eps: float = 1e-20
+    kind: str = field(init=False, default="routed_experts")
+
+    def __post_init__(self):
+        if not 1 <= self.top <= self.experts:
+            raise ConfigError(f"router: top={self.top} must lie in 1..experts={self.experts}")
 
 
 @dataclass(frozen=True)
@@ -163,6 +283,7 @@ class TokenEmbeddingSpec(PartSpec):
 
     vocab: int
     width: int
+    scale: float = 1.0   # every row is multiplied by this as it enters the residual stream
     kind: str = field(init=False, default="token_embedding")
 
 
@@ -174,6 +295,17 @@ class TokenPositionEmbeddingSpec(PartSpec):
     width: int
     max_positions: int
     kind: str = field(init=False, default="token_position_embedding")
+
+
+@dataclass(frozen=True)
+class PassEntrySpec(PartSpec):
+    """Entering pass t over a run of repeated layers: the embedding's output is added to the residual
+    again (`add_embedding`, every pass but the first) and then a learned vector `step[t]`."""
+
+    width: int
+    passes: int
+    add_embedding: bool = True
+    kind: str = field(init=False, default="pass_entry")
 
 
 @dataclass(frozen=True)
@@ -233,6 +365,8 @@ class LayerRun:
     layer: int
     cache: int
     writes_cache: bool = True
+    # a number t: before this run the model's pass entry (`ModelConfig.pass_entry`) is applied for pass t
+    enter: int | None = None
 
 
 @dataclass
@@ -252,6 +386,8 @@ class ModelConfig:
     # chosen by `kind`.  None: one table, and a plain (or tied) matrix, from the sizes above.
     embedding: PartSpec | None = None
     head: PartSpec | None = None
+    # what happens to the residual when a run opens a pass over repeated layers (`LayerRun.enter`)
+    pass_entry: PartSpec | None = None
 
     def __post_init__(self):
         if self.embedding is None:
@@ -272,6 +408,8 @@ class ModelConfig:
         for index, run in enumerate(self.order):
             if not 0 <= run.layer < len(self.layers):
                 raise ConfigError(f"run {index} names layer {run.layer}, model has {len(self.layers)}")
+            if run.enter is not None and self.pass_entry is None:
+                raise ConfigError(f"run {index} opens pass {run.enter} but the model has no pass entry")
             if run.writes_cache:
                 if run.cache in writers:
                     raise ConfigError(

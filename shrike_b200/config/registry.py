@@ -35,8 +35,9 @@ class TensorNames:
     layer_part: Callable[[int, str], str]
     embedding_prefix: str | None = None
     head_prefix: str | None = None
+    pass_entry_prefix: str = "pass_entry."   # before the parameters of `ModelConfig.pass_entry` (role "pass_entry")
     # (role, a part's own parameter name) -> the name's last piece in this architecture's files; None:
-    # the part's own names are the files' names.  Roles: a layer's roles, "final_norm", "embedding", "head".
+    # the part's own names are the files' names.  Roles: a layer's roles, "final_norm", "embedding", "head", "pass_entry".
     local_name: Callable[[str, str], str] | None = None
 
     def local(self, role: str, local: str) -> str:
@@ -47,6 +48,9 @@ class TensorNames:
 
     def final_norm_name(self, local: str) -> str:
         return self.final_norm_prefix + self.local("final_norm", local)
+
+    def pass_entry_name(self, local: str) -> str:
+        return self.pass_entry_prefix + self.local("pass_entry", local)
 
     def embedding_name(self, local: str) -> str:
         if local == "weight":

@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
   const int kv_head = head / (p.num_heads / p.num_kv_heads);
   const int* table = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
   const int rows_here = min(BM, q_len - tile_start);
-  const int lo = p.window > 0 ? max(0, pos0 + tile_start - p.window + 1) : 0;
+  const int lo = first_visible_key(pos0 + tile_start, p.window);
   const int hi = pos0 + tile_start + rows_here - 1;
   const int tile_lo = lo / PBN, tile_hi = hi / PBN;
 
@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
   for (int r = 0; r < 2; ++r) {
     const int t = tile_start + warp * 16 + (lane >> 2) + 8 * r;
     last[r] = t < q_len ? pos0 + t : -1;
-    first[r] = p.window > 0 ? max(0, last[r] - p.window + 1) : 0;
+    first[r] = first_visible_key(last[r], p.window);
   }
   float o[DTILES][4];
 #pragma unroll
@@ -443,7 +443,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int last_key = p.ctx_len[seq] - 1;
-  const int first_key = p.window > 0 ? max(0, last_key - p.window + 1) : 0;
+  const int first_key = first_visible_key(last_key, p.window);
   const int* table = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
   const int head0 = kv_head * group + row_tile * 16;
   const int rows_here = min(16, group - row_tile * 16);

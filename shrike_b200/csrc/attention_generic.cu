@@ -69,7 +69,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   const int start = q_start[seq];
   const int q_len = q_start[seq + 1] - start;
   const int last = ctx_len[seq] - q_len + (token - start);
-  const int first = window > 0 ? max(0, last - window + 1) : 0;
+  const int first = first_visible_key(last, window);
   const int* table = block_table + static_cast<size_t>(seq) * max_blocks;
   const float slope = slopes != nullptr ? slopes[head] : 0.f;
 

@@ -243,7 +243,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const int kv_head = head / (args.num_heads / args.num_kv_heads);
   // chain c owns rows tile_start + 128 c ...; rows_c <= 0: the chain has none
   const int rows_0 = min(BM, q_len - tile_start), rows_1 = min(BM, q_len - tile_start - BM);
-  const int lo = args.window > 0 ? max(0, pos0 + tile_start - args.window + 1) : 0;   // first key any row sees
+  const int lo = first_visible_key(pos0 + tile_start, args.window);   // first key any row sees
   const int hi_0 = pos0 + tile_start + rows_0 - 1;              // last key chain 0 sees
   const int hi_1 = rows_1 > 0 ? hi_0 + rows_1 : -1;
   const int hi = max(hi_0, hi_1);
@@ -425,7 +425,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int t = tile_start + chain * BM + row;
     const int my_steps = chain == 0 ? steps_0 : steps_1;
     const int last = t < q_len ? pos0 + t : -1;
-    const int first = args.window > 0 ? max(0, last - args.window + 1) : 0;
+    const int first = first_visible_key(last, args.window);
     const unsigned lane_base = static_cast<unsigned>(quarter * 32) << 16;
     const unsigned tmem_chain = sh->tmem_base + chain * CHAIN_COLS + lane_base, tmem_o = tmem_chain + O_COL;
     float row_max = -INFINITY, row_sum = 0.f;

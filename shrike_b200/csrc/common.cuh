@@ -149,10 +149,35 @@ template <> __device__ __forceinline__ float gelu_tanh_times<__nv_bfloat16>(floa
   return __fmul_rn(0.5f * g * (1.0f + t), u);
 }
 
-// Activation codes of the gated feed-forward, shared with the Python side.
-enum : int { SHRIKE_ACT_SILU = 0, SHRIKE_ACT_GELU_TANH = 1 };
-template <typename T> __device__ __forceinline__ float act_times(int act, float g, float u) {
+// The clamped gate: g <- min(g, limit), u <- clamp(u, -limit, limit), then g sigmoid(1.702 g) (u + 1), with one
+// rounding of the last product; the exponential as in silu_times.
+template <typename T> __device__ __forceinline__ float clamped_swish_times(float g, float u, float limit);
+template <> __device__ __forceinline__ float clamped_swish_times<float>(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return __fmul_rn(g / (1.0f + expf(-1.702f * g)), u + 1.0f);
+}
+template <> __device__ __forceinline__ float clamped_swish_times<__nv_bfloat16>(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return __fmul_rn(__fdividef(g, 1.0f + __expf(-1.702f * g)), u + 1.0f);
+}
+
+// Activation codes of the gated feed-forward, shared with the Python side.  `limit` serves the clamped gate alone.
+enum : int { SHRIKE_ACT_SILU = 0, SHRIKE_ACT_GELU_TANH = 1, SHRIKE_ACT_CLAMPED_SWISH = 2 };
+__host__ __device__ __forceinline__ bool known_activation(int act) { return act >= SHRIKE_ACT_SILU && act <= SHRIKE_ACT_CLAMPED_SWISH; }
+template <typename T> __device__ __forceinline__ float act_times(int act, float g, float u, float limit = 0.f) {
+  if (act == SHRIKE_ACT_CLAMPED_SWISH) return clamped_swish_times<T>(g, u, limit);
   return act == SHRIKE_ACT_GELU_TANH ? gelu_tanh_times<T>(g, u) : silu_times<T>(g, u);
+}
+
+// The first key a query at position `last` sees.  span > 0: the `span` latest keys (a sliding window);
+// span < 0: positions are cut into runs of -span counted from position 0, and a query sees its own run only;
+// span == 0: every key.  Never decreases as `last` grows, so a tile's first row gives the tile's first key.
+__host__ __device__ __forceinline__ int first_visible_key(int last, int span) {
+  if (span > 0) return last - span + 1 > 0 ? last - span + 1 : 0;
+  if (span < 0) return last > 0 ? (last / -span) * -span : 0;
+  return 0;
 }
 
 // base[0] + base[stride] + ... over `partials` slices (the stack a K-split product leaves),

@@ -15,7 +15,8 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int width, int vocab,
                              const int* __restrict__ previous, int previous_rows,
-                             const T* __restrict__ pos_table, const int* __restrict__ positions, int max_positions) {
+                             const T* __restrict__ pos_table, const int* __restrict__ positions, int max_positions,
+                             float scale, float* __restrict__ keep) {
   let_dependents_start();
   wait_for_previous();
   const int row = blockIdx.x;
@@ -25,36 +26,48 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
   if (!valid) id = 0;
   const T* src = table + static_cast<size_t>(id) * width;
   float* dst = out + static_cast<size_t>(row) * width;
+  float* kept = keep != nullptr ? keep + static_cast<size_t>(row) * width : nullptr;
   const T* pos_row = nullptr;
   if (pos_table != nullptr) {
     const int p = positions[row];
     if (p >= 0 && p < max_positions) pos_row = pos_table + static_cast<size_t>(p) * width;
   }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = valid ? to_float(src[i]) : 0.f;
+    float v = valid ? __fmul_rn(to_float(src[i]), scale) : 0.f;
     if (pos_row != nullptr) v = __fadd_rn(v, to_float(pos_row[i]));
     dst[i] = v;
+    if (kept != nullptr) kept[i] = v;
   }
 }
 
-// `pos_table` (same type as `table`) and `positions` may be null: a plain token embedding.
-SHRIKE_API int shrike_embed_positions(const int* ids, const void* table, int table_dtype, float* out, int n,
-                                      int width, int vocab, const int* previous, int previous_rows,
-                                      const void* pos_table, const int* positions, int max_positions,
-                                      cudaStream_t stream) {
+// `pos_table` (same type as `table`) and `positions` may be null: a plain token embedding.  Every table row is
+// multiplied by `scale` (float32) on its way; `keep` (may be null) receives a second copy of the result, for a
+// model that adds the embedding's output to the residual again later.
+SHRIKE_API int shrike_embed_scaled(const int* ids, const void* table, int table_dtype, float* out, int n,
+                                   int width, int vocab, const int* previous, int previous_rows,
+                                   const void* pos_table, const int* positions, int max_positions, float scale,
+                                   float* keep, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
   if (width <= 0 || vocab <= 0) return SHRIKE_BAD_ARGUMENT;
   if (pos_table != nullptr && (positions == nullptr || max_positions <= 0)) return SHRIKE_BAD_ARGUMENT;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == SHRIKE_F32)
     launch_dependent(embed_kernel<float>, n, threads, 0, stream, ids, static_cast<const float*>(table), out, width, vocab,
-                     previous, previous_rows, static_cast<const float*>(pos_table), positions, max_positions);
+                     previous, previous_rows, static_cast<const float*>(pos_table), positions, max_positions, scale, keep);
   else if (table_dtype == SHRIKE_BF16)
     launch_dependent(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, ids, static_cast<const __nv_bfloat16*>(table), out, width,
-                     vocab, previous, previous_rows, static_cast<const __nv_bfloat16*>(pos_table), positions, max_positions);
+                     vocab, previous, previous_rows, static_cast<const __nv_bfloat16*>(pos_table), positions, max_positions, scale, keep);
   else
     return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_embed_positions(const int* ids, const void* table, int table_dtype, float* out, int n,
+                                      int width, int vocab, const int* previous, int previous_rows,
+                                      const void* pos_table, const int* positions, int max_positions,
+                                      cudaStream_t stream) {
+  return shrike_embed_scaled(ids, table, table_dtype, out, n, width, vocab, previous, previous_rows, pos_table, positions,
+                             max_positions, 1.0f, nullptr, stream);
 }
 
 SHRIKE_API int shrike_embed(const int* ids, const void* table, int table_dtype, float* out, int n,
@@ -246,7 +259,7 @@ SHRIKE_API int shrike_add_rmsnorm(float* resid, const void* delta, int delta_dty
 // (the order in which a fused gate/up matrix keeps its rows for the tensor-core product's own
 // activation epilogue); b is a multiple of VEC.
 template <typename T, int VEC>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int rows, int block, int act) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int rows, int block, int act, float limit) {
   let_dependents_start();
   wait_for_previous();
   // blockIdx.y walks the rows, blockIdx.x and the threads a row's groups of VEC columns: no division
@@ -277,7 +290,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
         if (group >= groups_per_row) continue;
         Pack r;
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(act_times<T>(act, to_float(g[k].v[j]), to_float(u[k].v[j])));
+        for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(act_times<T>(act, to_float(g[k].v[j]), to_float(u[k].v[j]), limit));
         *reinterpret_cast<Pack*>(out_row + group * VEC) = r;
       }
     }
@@ -288,7 +301,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 // whole run pair, 64 contiguous bytes in and 32 out, so a warp reads 2 KiB in one piece.  (With a
 // thread per 16-byte group the gate loads of a warp touch every other 32 bytes, the up loads the
 // rest: the same bytes, twice the lines per instruction.)
-__global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, int rows, int act) {
+__global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, int rows, int act, float limit) {
   let_dependents_start();
   wait_for_previous();
   const int runs_per_row = inter / 16;
@@ -307,7 +320,7 @@ __global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up
         uint4 packed;
         __nv_bfloat16* r = reinterpret_cast<__nv_bfloat16*>(&packed);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) r[j] = from_float<__nv_bfloat16>(act_times<__nv_bfloat16>(act, to_float(g[j]), to_float(u[j])));
+        for (int j = 0; j < 8; ++j) r[j] = from_float<__nv_bfloat16>(act_times<__nv_bfloat16>(act, to_float(g[j]), to_float(u[j]), limit));
         out_row[run * 2 + half] = packed;
       }
     }
@@ -315,13 +328,13 @@ __global__ void silu_mul_runs16_kernel(const __nv_bfloat16* __restrict__ gate_up
 }
 
 template <typename T>
-static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, int block, int act, cudaStream_t stream) {
+static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, int block, int act, float limit, cudaStream_t stream) {
   if (sizeof(T) == 2 && block == 16 && inter % 16 == 0 &&
       (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
     const int threads = 256, runs_per_row = inter / 16;
     const dim3 grid(max(1, min(64, (runs_per_row + threads - 1) / threads)), max(1, min(n, 65535)));
     launch_dependent(silu_mul_runs16_kernel, grid, threads, 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
-                     static_cast<__nv_bfloat16*>(out), inter, n, act);
+                     static_cast<__nv_bfloat16*>(out), inter, n, act, limit);
     return;
   }
   constexpr int WIDE = 16 / sizeof(T);
@@ -335,22 +348,29 @@ static void launch_silu_mul(const void* gate_up, void* out, int n, int inter, in
   const dim3 grid(across, down);
   if (vec)
     launch_dependent(silu_mul_kernel<T, WIDE>, grid, threads, 0, stream, static_cast<const T*>(gate_up),
-                     static_cast<T*>(out), inter, n, block, act);
+                     static_cast<T*>(out), inter, n, block, act, limit);
   else
     launch_dependent(silu_mul_kernel<T, 1>, grid, threads, 0, stream, static_cast<const T*>(gate_up),
-                     static_cast<T*>(out), inter, n, block, act);
+                     static_cast<T*>(out), inter, n, block, act, limit);
 }
 
-// out = act(gate) * up with `act` one of SHRIKE_ACT_*; the layout of gate_up as for shrike_silu_mul.
-SHRIKE_API int shrike_act_mul(const void* gate_up, void* out, int dtype, int n, int inter, int block, int act,
-                              cudaStream_t stream) {
+// out = act(gate) * up with `act` one of SHRIKE_ACT_* (`limit`: the clamp of SHRIKE_ACT_CLAMPED_SWISH); the layout
+// of gate_up as for shrike_silu_mul.
+SHRIKE_API int shrike_act_mul_limit(const void* gate_up, void* out, int dtype, int n, int inter, int block, int act,
+                                    float limit, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
   if (inter <= 0 || block < 0 || (block > 0 && inter % block)) return SHRIKE_BAD_ARGUMENT;
-  if (act != SHRIKE_ACT_SILU && act != SHRIKE_ACT_GELU_TANH) return SHRIKE_BAD_ARGUMENT;
-  if (dtype == SHRIKE_F32) launch_silu_mul<float>(gate_up, out, n, inter, block, act, stream);
-  else if (dtype == SHRIKE_BF16) launch_silu_mul<__nv_bfloat16>(gate_up, out, n, inter, block, act, stream);
+  if (!known_activation(act)) return SHRIKE_BAD_ARGUMENT;
+  if (dtype == SHRIKE_F32) launch_silu_mul<float>(gate_up, out, n, inter, block, act, limit, stream);
+  else if (dtype == SHRIKE_BF16) launch_silu_mul<__nv_bfloat16>(gate_up, out, n, inter, block, act, limit, stream);
   else return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_act_mul(const void* gate_up, void* out, int dtype, int n, int inter, int block, int act,
+                              cudaStream_t stream) {
+  if (act == SHRIKE_ACT_CLAMPED_SWISH) return SHRIKE_BAD_ARGUMENT;   // that one needs its limit
+  return shrike_act_mul_limit(gate_up, out, dtype, n, inter, block, act, 0.f, stream);
 }
 
 SHRIKE_API int shrike_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, int block, cudaStream_t stream) {

@@ -70,6 +70,7 @@ struct Args {
   int kblocks_per_split, stages, out_dtype;
   int gated;            // nonzero (1 + activation code): the weight rows come in runs of 16 gate rows and the 16 up
                         // rows of the same features; out is [T][N / 2] bfloat16 = act(gate) * up
+  float act_limit;      // the clamp of the activation SHRIKE_ACT_CLAMPED_SWISH
 };
 
 __global__ void __launch_bounds__(THREADS, 3)
@@ -199,7 +200,7 @@ gemm_swap_ab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const int t = t0 + c0 + j + (lane < 16 ? 0 : 8);
           if (t < args.tokens && n0 + quarter * 32 + lane < args.n)
             static_cast<__nv_bfloat16*>(args.out)[static_cast<size_t>(t) * half_n + feature] =
-                __float2bfloat16_rn(act_times<__nv_bfloat16>(args.gated - 1, gate, up));
+                __float2bfloat16_rn(act_times<__nv_bfloat16>(args.gated - 1, gate, up, args.act_limit));
         }
       }
     } else if (ok) {
@@ -265,7 +266,7 @@ SHRIKE_API int shrike_gemm_tc_splits(int tokens, int n, int k) {
 // strides) and both 16-byte aligned.  splits == 1: out is [tokens, n] of out_dtype.
 // splits > 1 (as shrike_gemm_tc_splits says): out is [splits, tokens, n] float32.
 static int launch_gemm_tc(const void* x, const void* w, const float* bias, void* out, int out_dtype, int tokens,
-                          int n, int k, int splits, int gated, int* status, cudaStream_t stream) {
+                          int n, int k, int splits, int gated, int* status, cudaStream_t stream, float act_limit = 0.f) {
   using namespace tc;
   if (tokens <= 0 || n <= 0) return SHRIKE_OK;
   if (k <= 0 || k % 8 || splits < 1 || (out_dtype != SHRIKE_F32 && out_dtype != SHRIKE_BF16)) return SHRIKE_BAD_ARGUMENT;
@@ -312,6 +313,7 @@ static int launch_gemm_tc(const void* x, const void* w, const float* bias, void*
   args.kblocks_per_split = per_split;
   args.stages = stages;
   args.gated = gated;
+  args.act_limit = act_limit;
   args.out_dtype = out_dtype;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3((n + BM - 1) / BM, splits, token_tiles);
@@ -347,4 +349,11 @@ SHRIKE_API int shrike_gemm_tc_gated_act(const void* x, const void* w, void* out,
                                         int* status, cudaStream_t stream) {
   if (n % 32 || (act != SHRIKE_ACT_SILU && act != SHRIKE_ACT_GELU_TANH)) return SHRIKE_BAD_ARGUMENT;
   return launch_gemm_tc(x, w, nullptr, out, SHRIKE_BF16, tokens, n, k, 1, 1 + act, status, stream);
+}
+
+// The same for an activation with a parameter (`limit`: the clamp of SHRIKE_ACT_CLAMPED_SWISH).
+SHRIKE_API int shrike_gemm_tc_gated_act_limit(const void* x, const void* w, void* out, int tokens, int n, int k, int act,
+                                              float limit, int* status, cudaStream_t stream) {
+  if (n % 32 || !known_activation(act)) return SHRIKE_BAD_ARGUMENT;
+  return launch_gemm_tc(x, w, nullptr, out, SHRIKE_BF16, tokens, n, k, 1, 1 + act, status, stream, limit);
 }

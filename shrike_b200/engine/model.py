@@ -79,6 +79,13 @@ class DecoderModel:
             if hasattr(self.blocks[-1], "prepare"):
                 self.blocks[-1].prepare()
             parts += [*built.values(), self.blocks[-1]]
+        self.pass_entry = None
+        if config.pass_entry is not None:
+            spec = config.pass_entry
+            cls = part_class("pass_entry", spec.kind)
+            self.pass_entry = cls(spec, {local: tensors[names.pass_entry_name(local)] for local in cls.parameters(spec)},
+                                  ops, runtime)
+            parts.append(self.pass_entry)
         norm = config.final_norm
         cls = part_class("norm", norm.kind)
         self.final_norm = cls(norm, {local: tensors[names.final_norm_name(local)] for local in cls.parameters(norm)},
@@ -136,9 +143,15 @@ class DecoderModel:
     def forward(self, ctx) -> torch.Tensor:
         """float32 logits [R, vocab] at `ctx.out_rows`."""
         ctx.carried.clear()   # nothing is carried from one forward pass to the next
+        if self.pass_entry is not None:
+            self.pass_entry.before_embedding(ctx)   # it may ask the embedding for a second copy of its output
         resid = self.embedding.forward(ctx)
         delta = None
+        if self.pass_entry is not None:
+            self.pass_entry.begin(resid, ctx)   # it keeps what it needs of the embedding's output
         for run in self.config.order:
+            if run.enter is not None:
+                resid, delta = self.pass_entry.forward(resid, delta, ctx, run.enter)
             resid, delta = self.blocks[run.layer].forward(resid, delta, ctx, run)
         if not ctx.num_rows:
             return self.runtime.buffer("logits", (0, self.config.vocab_size), torch.float32)

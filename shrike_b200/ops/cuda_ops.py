@@ -103,6 +103,8 @@ class CudaOps:
             self.gemm_tc.shrike_gemm_tc_gated.restype = _I
             self.gemm_tc.shrike_gemm_tc_gated_act.argtypes = [_P, _P, _P, _I, _I, _I, _I, _P, _P]
             self.gemm_tc.shrike_gemm_tc_gated_act.restype = _I
+            self.gemm_tc.shrike_gemm_tc_gated_act_limit.argtypes = [_P, _P, _P, _I, _I, _I, _I, _F, _P, _P]
+            self.gemm_tc.shrike_gemm_tc_gated_act_limit.restype = _I
             self.gemm_tc.shrike_gemm_tc_splits.argtypes = [_I, _I, _I]
             self.gemm_tc.shrike_gemm_tc_splits.restype = _I
         self._scratch = None     # partial results of split single-token attention
@@ -138,6 +140,17 @@ class CudaOps:
         lib.shrike_qk_norm_store.argtypes = [_P, _I, _LL, _P, _P, _F, _P, _F, _I, _P, _P, _P, _P] + [_I] * 6 + [_LL, _P]
         lib.shrike_latent_store.argtypes = [_P, _I, _LL, _P, _F, _P, _P, _P, _P] + [_I] * 7 + [_LL, _P]
         lib.shrike_head_scale.argtypes = [_P, _P, _I, _I, _I, _I, _P]
+        lib.shrike_embed_scaled.argtypes = [_P, _P, _I, _P, _I, _I, _I, _P, _I, _P, _P, _I, _F, _P, _P]
+        lib.shrike_act_mul_limit.argtypes = [_P, _P, _I, _I, _I, _I, _I, _F, _P]
+        lib.shrike_tanh_norm.argtypes = [_P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P]
+        lib.shrike_head_prep.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P] + [_I] * 8 + [_P]
+        lib.shrike_matrix_memory_scan.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P, _P] + [_I] * 5 + [_F, _F, _F, _P]
+        lib.shrike_matrix_memory_out.argtypes = [_P, _P, _P, _I, _LL, _I, _I, _P, _F, _P, _I, _I, _I, _I, _P]
+        lib.shrike_route_top.argtypes = [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]
+        lib.shrike_act_mul_blocks.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P]
+        for name in ("shrike_embed_scaled", "shrike_act_mul_limit", "shrike_tanh_norm", "shrike_head_prep",
+                     "shrike_matrix_memory_scan", "shrike_matrix_memory_out", "shrike_route_top", "shrike_act_mul_blocks"):
+            getattr(lib, name).restype = _I
         lib.shrike_sample_slices.argtypes = [_I]
         lib.shrike_sample_slices.restype = _I
         for name in ("shrike_embed", "shrike_add_rmsnorm", "shrike_silu_mul", "shrike_rope_kv_write",
@@ -214,10 +227,11 @@ class CudaOps:
         return self._layer_program
 
     # ---- kernels ------------------------------------------------------------
-    def embed(self, ids, table, out, previous=None, position_table=None, positions=None):
-        """Rows of `table` into the float32 residual.  An id of -1 - r is replaced on the device
-        by `previous[r]` (int32: the tokens the step before drew).  With `position_table`
-        ([max positions, width], the type of `table`) the row of each token's position is added."""
+    def embed(self, ids, table, out, previous=None, position_table=None, positions=None, scale=1.0, keep=None):
+        """Rows of `table`, each times `scale`, into the float32 residual.  An id of -1 - r is replaced on
+        the device by `previous[r]` (int32: the tokens the step before drew).  With `position_table`
+        ([max positions, width], the type of `table`) the row of each token's position is added.
+        `keep` (float32, the shape of `out`) receives a second copy of the result."""
         _dense(ids, torch.int32, "token ids")
         _dense(out, torch.float32, "residual")
         n, width = out.shape
@@ -228,11 +242,15 @@ class CudaOps:
             _dense(positions, torch.int32, "positions")
             if position_table.shape[1] != width:
                 raise KernelError("the position table's rows must be as wide as the residual")
+        if keep is not None:
+            _dense(keep, torch.float32, "kept embedding")
+            if tuple(keep.shape) != tuple(out.shape):
+                raise KernelError("the kept copy must have the residual's shape")
         self.launches += 1
-        _check(self.core.shrike_embed_positions(
+        _check(self.core.shrike_embed_scaled(
             _ptr(ids), _ptr(table), _DTYPE_CODE[table.dtype], _ptr(out), n, width, table.shape[0], _ptr(previous),
             0 if previous is None else previous.numel(), _ptr(position_table), _ptr(positions),
-            0 if position_table is None else position_table.shape[0], self._stream()), "embed")
+            0 if position_table is None else position_table.shape[0], float(scale), _ptr(keep), self._stream()), "embed")
 
     @staticmethod
     def _stack(delta):
@@ -462,8 +480,10 @@ class CudaOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None):
-        """Attention of the batch's new tokens over the paged cache.  `max_q_len` and
+                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None, chunk=None):
+        """Attention of the batch's new tokens over the paged cache.  `window`: a query sees the `window`
+        latest keys.  `chunk` (instead of a window): a query at position p sees key j <= p only when
+        floor(p / chunk) = floor(j / chunk).  `max_q_len` and
         `min_q_len` are the longest and shortest entry of the batch (0: not known); `q_lens`, every
         entry's length (host list), lets the portions kernel launch exactly the CTAs it needs.
         `softcap` (a positive number) and `slopes` (float32 [num_heads]) change a score
@@ -478,6 +498,10 @@ class CudaOps:
         lib = self._attention_lib(head_dim)
         num_seqs, max_blocks = block_table.shape
         page_size, num_pages = keys.shape[1], keys.shape[0]
+        if chunk:
+            if window:
+                raise KernelError("attention takes a window or a chunk, not both")
+            window = -int(chunk)   # the kernels' one number: > 0 a window, < 0 runs of that many positions
         if self.dtype == torch.float32 or head_dim > build.TENSOR_CORE_HEAD_DIM:
             self.launches += 1
             _check(lib.shrike_paged_attention_generic(
@@ -587,21 +611,31 @@ class CudaOps:
             return cluster, cluster
         return min(want // cluster * cluster, 32 * cluster), cluster
 
-    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}   # the codes the kernels take
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}   # the codes the kernels take
 
     def silu_mul(self, gate_up, out, block=0):
         """out = silu(gate) * up; see `act_mul`."""
         self.act_mul(gate_up, out, block, "silu")
 
-    def act_mul(self, gate_up, out, block=0, activation="silu"):
+    def act_mul(self, gate_up, out, block=0, activation="silu", limit=None):
         """out = act(gate) * up, act one of `ACTIVATIONS`.  `block` 0: a row of gate_up is all gate columns,
-        then all up columns; b > 0: runs of b gate columns, each followed by the b up columns of the same features."""
+        then all up columns; b > 0: runs of b gate columns, each followed by the b up columns of the same features.
+        `clamped_swish` with `limit` L is min(g, L) * sigmoid(1.702 min(g, L)) * (clamp(u, -L, L) + 1)."""
         _dense(gate_up, self.dtype, "gate_up")
         _dense(out, self.dtype, "activation")
         n, inter = out.shape
         self.launches += 1
-        _check(self.core.shrike_act_mul(_ptr(gate_up), _ptr(out), self.code, n, inter, block,
-                                        self.ACTIVATIONS[activation], self._stream()), "act_mul")
+        _check(self.core.shrike_act_mul_limit(_ptr(gate_up), _ptr(out), self.code, n, inter, block,
+                                              self.ACTIVATIONS[activation], self._limit(activation, limit), self._stream()),
+               "act_mul")
+
+    @staticmethod
+    def _limit(activation, limit) -> float:
+        if activation == "clamped_swish":
+            if limit is None or not limit > 0:
+                raise KernelError("the clamped activation needs a positive limit")
+            return float(limit)
+        return 0.0
 
     @property
     def gated_rows(self) -> int:
@@ -610,7 +644,7 @@ class CudaOps:
         features.  0: keep gate rows, then up rows (no fused activation in this mode)."""
         return 16 if self.dtype == torch.bfloat16 and self.gemm_tc is not None else 0
 
-    def linear_gated(self, x, w, out, activation="silu") -> bool:
+    def linear_gated(self, x, w, out, activation="silu", limit=None) -> bool:
         """act(x Wg^T) * (x Wu^T) into `out` [N, I] in one kernel, for `w` [2 I, K] interleaved as
         `gated_rows` says.  Returns False when this shape is not served (many tokens: the caller
         then runs the product and the activation kernel, the latter with block=gated_rows)."""
@@ -623,10 +657,117 @@ class CudaOps:
         _dense(w, torch.bfloat16, "linear weight")
         _dense(out, torch.bfloat16, "activation")
         self.launches += 1
-        _check(self.gemm_tc.shrike_gemm_tc_gated_act(_ptr(x), _ptr(w), _ptr(out), n, rows, k,
-                                                     self.ACTIVATIONS[activation], _ptr(self.status), self._stream()),
+        _check(self.gemm_tc.shrike_gemm_tc_gated_act_limit(_ptr(x), _ptr(w), _ptr(out), n, rows, k,
+                                                           self.ACTIVATIONS[activation], self._limit(activation, limit),
+                                                           _ptr(self.status), self._stream()),
                "gemm_tcgen05")
         return True
+
+    def tanh_norm(self, resid, terms=(), row_add=None, rows=None, norms=()):
+        """resid += sum over `terms` of scale * pending (each `(tensor, scale)`, the tensor float32 [N, W] or
+        a K-split stack [P, N, W]) + `row_add` (float32 [W], added to every row); then, for each of up to two
+        `norms` `(alpha, weight, bias, out)`, out = tanh(alpha x) * weight + bias of the summed row.  With
+        `rows` (int32 [R]) only `out[r]` for row rows[r] is written, the residual stays."""
+        _dense(resid, torch.float32, "residual")
+        n, width = resid.shape
+        if len(terms) > 4 or len(norms) > 2:
+            raise KernelError("tanh_norm takes at most four pending sums and two norms")
+        count = rows.shape[0] if rows is not None else n
+        data = (_P * 4)()
+        partials, strides, scales = (_I * 4)(), (_LL * 4)(), (_F * 4)()
+        for index, (tensor, scale) in enumerate(terms):
+            _dense(tensor, torch.float32, "pending sum")
+            if tuple(tensor.shape[-2:]) != (n, width):
+                raise KernelError(f"pending sum {tuple(tensor.shape)} does not fit the residual {tuple(resid.shape)}")
+            data[index] = tensor.data_ptr()
+            partials[index], strides[index] = self._stack(tensor)
+            scales[index] = float(scale)
+        alpha, weight, bias, out = (_F * 2)(), (_P * 2)(), (_P * 2)(), (_P * 2)()
+        out_code = 0
+        for index, (a, w, b, o) in enumerate(norms):
+            _dense(w, torch.float32, "norm weight")
+            _dense(b, torch.float32, "norm bias")
+            if tuple(o.shape) != (count, width) or not o.is_contiguous():
+                raise KernelError(f"norm output {tuple(o.shape)} does not fit {count} rows of {width}")
+            alpha[index], weight[index], bias[index], out[index] = float(a), w.data_ptr(), b.data_ptr(), o.data_ptr()
+            out_code = _DTYPE_CODE[o.dtype]
+        if rows is not None:
+            _dense(rows, torch.int32, "rows")
+        self.launches += 1
+        _check(self.core.shrike_tanh_norm(_ptr(resid), data, partials, strides, scales, len(terms), _ptr(row_add), _ptr(rows),
+                                          len(norms), alpha, weight, bias, out, out_code, count, width, self._stream()),
+               "tanh_norm")
+
+    def head_prep(self, fused, bias, positions, inv_freq, rot, q_weight, k_weight, eps, q_out, keys, values, slots,
+                  gate_out, num_heads, num_kv_heads, dim, vdim, padded):
+        """A fused q|k|v(|gate) projection ([N, total] float32 or a K-split stack) made ready for paged
+        attention: `bias` ([total] or None) added; q and k divided by their root mean square per head and
+        scaled by `q_weight` / `k_weight` ([dim], None: left as they are); the first `rot` dimensions of
+        every q and k head rotated, dimension i with i + rot/2, by position * inv_freq[i]; q to `q_out`
+        [N, H * padded], k and v into their pages, heads `padded` elements apart (padding zeroed); with
+        `gate_out` (float32 [N, H]) the sigmoid of the last H columns."""
+        _dense(fused, torch.float32, "fused projection")
+        _dense(q_out, self.dtype, "q")
+        partials, stride = self._stack(fused)
+        num_slots = 0
+        if keys is not None:
+            _dense(keys, self.dtype, "key cache")
+            _dense(values, self.dtype, "value cache")
+            num_slots = keys.shape[0] * keys.shape[1]
+        self.launches += 1
+        _check(self.core.shrike_head_prep(
+            _ptr(fused), partials, stride, fused.shape[-1], _ptr(bias), _ptr(positions), _ptr(inv_freq), rot if inv_freq is not None else 0,
+            _ptr(q_weight), _ptr(k_weight), eps, _ptr(q_out), _ptr(keys), _ptr(values), _ptr(slots), _ptr(gate_out),
+            self.code, fused.shape[-2], num_heads, num_kv_heads, dim, vdim, padded, num_slots, self._stream()), "head_prep")
+
+    def matrix_memory(self, fused, gate_bias, state, q_start, state_slot, numerator, denominator, weight, eps, out,
+                      num_seqs, num_heads, dim, vdim, cap, floor):
+        """The matrix-memory recurrence over the batch's new tokens and its gated, normed output.
+
+        `fused` ([N, total] float32 or a K-split stack): q (H dim) | k (H dim) | v (H vdim) | output gate
+        (H vdim) | input gate (H) | forget gate (H); `gate_bias` float32 [2 H].  `state` float32
+        [slots, H, dim * vdim + dim + 1] (S, z, m of every head) is read and left updated for the slots
+        `state_slot` names (-1: the sequence is skipped).  `out` [N, H * vdim]: each head's o over its root
+        mean square, times `weight`, times the sigmoid of the output gate."""
+        _dense(fused, torch.float32, "fused projection")
+        _dense(state, torch.float32, "state")
+        _dense(out, self.dtype, "mixer output")
+        partials, stride = self._stack(fused)
+        total, n = fused.shape[-1], fused.shape[-2]
+        if tuple(state.shape[1:]) != (num_heads, dim * vdim + dim + 1):
+            raise KernelError(f"state {tuple(state.shape)} does not fit {num_heads} heads of {dim} x {vdim}")
+        self.launches += 2
+        _check(self.core.shrike_matrix_memory_scan(
+            _ptr(fused), partials, stride, total, _ptr(gate_bias), _ptr(state), _ptr(q_start), _ptr(state_slot),
+            _ptr(numerator), _ptr(denominator), num_seqs, num_heads, dim, vdim, state.shape[0], cap, float(dim) ** -0.5, floor,
+            self._stream()), "matrix_memory_scan")
+        _check(self.core.shrike_matrix_memory_out(
+            _ptr(numerator), _ptr(denominator), _ptr(fused), partials, stride, total, 2 * num_heads * dim + num_heads * vdim,
+            _ptr(weight), eps, _ptr(out), self.code, n, num_heads, vdim, self._stream()), "matrix_memory_out")
+
+    def route_top(self, x, router, shared_gate, weights, top, renorm_eps):
+        """weights [N, E (+ 1)] float32: softmax(router x) over all E experts in 32-bit, the `top` largest
+        divided by their sum (+ renorm_eps), 0 elsewhere; a last column, when there is one, holds
+        sigmoid(shared_gate . x) (1 when `shared_gate` is None)."""
+        _dense(x, self.dtype, "router input")
+        _dense(router, torch.float32, "router weight")
+        _dense(weights, torch.float32, "expert weights")
+        self.launches += 1
+        _check(self.core.shrike_route_top(_ptr(x), self.code, _ptr(router), _ptr(shared_gate), _ptr(weights), x.shape[0], x.shape[1],
+                                          router.shape[0], top, weights.shape[1], renorm_eps, self._stream()), "route_top")
+
+    def act_mul_blocks(self, gate_up, weights, out, experts, each, activation="silu", limit=None):
+        """out[n, c] = act(gate[n, c]) * up[n, c] * weights[n, e(c)] for gate_up [N, 2 I] (gate columns, then up
+        columns): column c belongs to expert c // each while c < experts * each, else to the shared expert
+        (the last column of `weights`)."""
+        _dense(gate_up, self.dtype, "gate_up")
+        _dense(out, self.dtype, "activation")
+        _dense(weights, torch.float32, "expert weights")
+        n, inter = out.shape
+        self.launches += 1
+        _check(self.core.shrike_act_mul_blocks(_ptr(gate_up), _ptr(weights), _ptr(out), self.code, n, inter, experts, each,
+                                               weights.shape[1], self.ACTIVATIONS[activation], self._limit(activation, limit),
+                                               self._stream()), "act_mul_blocks")
 
     def sample(self, logits, temperature, top_p, seeds, out):
         _dense(logits, torch.float32, "logits")

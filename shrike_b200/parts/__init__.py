@@ -1,6 +1,6 @@
 """Parts a layer is put together from.  Importing the package registers the built-in ones."""
 
-from . import attention, block, embedding, latent_attention, mlp, norm, rotary  # noqa: F401
+from . import attention, block, embedding, experts, latent_attention, matrix_memory, mlp, norm, parallel, rotary  # noqa: F401
 from .base import (  # noqa: F401
     BLOCKS,
     EMBEDDINGS,
@@ -11,6 +11,7 @@ from .base import (  # noqa: F401
     POSITIONS,
     KVNeed,
     ParamSpec,
+    PendingSum,
     StateNeed,
     part_class,
     register_part,

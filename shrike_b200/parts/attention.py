@@ -14,6 +14,10 @@ and portions alike.  Optional `window`: a query sees only the `window` latest ke
 projection, no value projection and no rotation; queries and keys normed over the whole projection,
 a query temperature that grows with the logarithm of the position, scores soft-capped and biased
 by distance, a key window.  Each of these is a parameter of its spec.
+
+`GatedHeadAttention` adds, each as an option of its spec: a norm of q and k per head, a rotation of
+part of each head, chunks of positions in place of a window, keys and values of different sizes and a
+sigmoid gate per head on the output.
 """
 
 from __future__ import annotations
@@ -182,5 +186,103 @@ class SharedKeyValueAttention:
         return ops.linear(attn, self.w_o, delta, allow_partials=True)
 
 
+class GatedHeadAttention:
+    """Grouped-query attention with the options of `GatedHeadAttentionSpec`: biases, a root-mean-square
+    norm of q and k per head with one weight for all heads, a rotation of each head's first
+    dimensions, a window or chunks of positions, an output gate per head.  q, k, v and the gate are
+    one matrix product; one kernel turns its 32-bit result into queries and cache rows; the paged
+    attention kernels run as they are (a chunk is handed to them as a negative window).  Keys and
+    values share the pages' head size, the next multiple of 16 above the larger of the two; the
+    columns so added meet zeros in q, the pages and `o_proj`."""
+
+    capture_safe = True
+
+    @staticmethod
+    def parameters(spec) -> dict[str, ParamSpec]:
+        q_out, k_out, v_out = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.num_kv_heads * spec.value_dim
+        params = {
+            "q_proj.weight": ParamSpec((q_out, spec.width), "matrix"),
+            "k_proj.weight": ParamSpec((k_out, spec.width), "matrix"),
+            "v_proj.weight": ParamSpec((v_out, spec.width), "matrix"),
+            "o_proj.weight": ParamSpec((spec.width, spec.num_heads * spec.value_dim), "matrix"),
+        }
+        if spec.qkv_bias:
+            params["q_proj.bias"] = ParamSpec((q_out,), "bias")
+            params["k_proj.bias"] = ParamSpec((k_out,), "bias")
+            params["v_proj.bias"] = ParamSpec((v_out,), "bias")
+        if spec.out_bias:
+            params["o_proj.bias"] = ParamSpec((spec.width,), "bias")
+        if spec.qk_norm:
+            params["q_norm.weight"] = ParamSpec((spec.head_dim,), "norm")
+            params["k_norm.weight"] = ParamSpec((spec.head_dim,), "norm")
+        if spec.head_gate:
+            params["gate.weight"] = ParamSpec((spec.num_heads, spec.width), "matrix")
+        return params
+
+    @staticmethod
+    def cache_needs(spec) -> list:
+        return [KVNeed(spec.num_kv_heads, padded_head(max(spec.head_dim, spec.value_dim)), spec.window, chunk=spec.chunk)]
+
+    def __init__(self, spec, tensors, ops, runtime):
+        self.spec, self.ops, self.runtime = spec, ops, runtime
+        self.padded = padded_head(max(spec.head_dim, spec.value_dim))
+        ops.check_head_dim(self.padded)
+        rows = [tensors.pop("q_proj.weight"), tensors.pop("k_proj.weight"), tensors.pop("v_proj.weight")]
+        if spec.head_gate:
+            rows.append(tensors.pop("gate.weight").to(rows[0].dtype))
+        self.w_fused = torch.cat(rows).contiguous()
+        self.total = self.w_fused.shape[0]
+        self.bias = None
+        if spec.qkv_bias:
+            bias = torch.zeros(self.total, dtype=torch.float32, device=self.w_fused.device)   # the gate has none
+            given = torch.cat([tensors.pop("q_proj.bias"), tensors.pop("k_proj.bias"), tensors.pop("v_proj.bias")])
+            bias[: given.numel()] = given.to(torch.float32)
+            self.bias = bias
+        w_o = tensors.pop("o_proj.weight")
+        if self.padded != spec.value_dim:   # the kernels' heads are wider: the added columns meet zeros
+            wide = w_o.new_zeros(spec.width, spec.num_heads, self.padded)
+            wide[:, :, : spec.value_dim] = w_o.view(spec.width, spec.num_heads, spec.value_dim)
+            w_o = wide.view(spec.width, spec.num_heads * self.padded)
+        self.w_o = w_o.contiguous()
+        self.b_o = tensors.pop("o_proj.bias").to(torch.float32).contiguous() if spec.out_bias else None
+        self.q_weight = self.k_weight = None
+        if spec.qk_norm:
+            self.q_weight = tensors.pop("q_norm.weight").to(torch.float32).contiguous()
+            self.k_weight = tensors.pop("k_norm.weight").to(torch.float32).contiguous()
+        self.inv_freq, self.rot = None, 0
+        if spec.rotary is not None:
+            dims, base = spec.rotary
+            table = torch.tensor([float(base) ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64)
+            self.inv_freq, self.rot = table.to(torch.float32).to(runtime.device), int(dims)
+        self.out_width = spec.num_heads * self.padded
+
+    def forward(self, x, ctx, run):
+        spec, rt, ops = self.spec, self.runtime, self.ops
+        n = x.shape[0]
+        fused = rt.buffer("qkv", (n, self.total), torch.float32)
+        fused = ops.linear(x, self.w_fused, fused, allow_partials=True)
+        group, keys, values = ctx.storage.keys_values(run.cache)
+        view = ctx.groups[group]
+        q = rt.buffer("q", (n, self.out_width), rt.act_dtype)
+        gate = rt.buffer("head_gate", (n, spec.num_heads), torch.float32) if spec.head_gate else None
+        ops.head_prep(
+            fused, self.bias, ctx.positions, self.inv_freq, self.rot, self.q_weight, self.k_weight, spec.eps, q,
+            keys if run.writes_cache else None, values if run.writes_cache else None, view.slot_mapping, gate,
+            spec.num_heads, spec.num_kv_heads, spec.head_dim, spec.value_dim, self.padded,
+        )
+        attn = rt.buffer("attn_out", (n, self.out_width), rt.act_dtype)
+        ops.paged_attention(
+            q, keys, values, view.block_table, ctx.q_start, ctx.ctx_len, ctx.seq_of_token,
+            spec.num_heads, spec.num_kv_heads, self.padded, spec.scale, spec.window, attn,
+            max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, min_q_len=ctx.min_q_len, q_lens=ctx.q_lens,
+            **({"chunk": spec.chunk} if spec.chunk is not None else {}),
+        )
+        if gate is not None:
+            ops.head_scale(attn, gate, spec.num_heads, self.padded)
+        delta = rt.buffer("mixer_delta", (n, spec.width), torch.float32)
+        return ops.linear(attn, self.w_o, delta, bias=self.b_o, allow_partials=True)
+
+
 register_part("mixer", "attention", PagedAttention)
+register_part("mixer", "gated_head_attention", GatedHeadAttention)
 register_part("mixer", "shared_kv_attention", SharedKeyValueAttention)

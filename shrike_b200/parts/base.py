@@ -37,6 +37,11 @@ be checked and the cache sized before anything is put on the device):
       forward(ctx) -> resid_f32[N,W]   the residual stream of the step's tokens.  A token id of
           -1 - r stands for `ctx.previous_tokens[r]` (what the step before drew in its row r).
       `table`: the [vocab, W] tensor a tied head may share, or None
+  pass entry (a model whose run order repeats layers may have one; `LayerRun.enter` = t calls it)
+      before_embedding(ctx)            may put a float32 buffer into ctx.carried["embedding_copy"]; an embedding
+                                       that fills it says so with ctx.carried["embedding_copied"] = True
+      begin(resid_f32, ctx)            right after the embedding: keeps what later passes need of it
+      forward(resid_f32, delta, ctx, t) -> (resid_f32, delta)   what entering pass t does to the residual
   head
       forward(hidden[R,W]) -> float32 logits [R, vocab]   (hidden: the final norm's output on the
           wanted rows); built with tensors {"weight": ...}, the embedding's table when tied
@@ -67,12 +72,15 @@ class ParamSpec:
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values in pages: `window` None keeps all, else the last `window`.  `planes` 2: a key
-    and a value tensor; 1: one tensor a token (a latent that serves as both), at half the memory."""
+    and a value tensor; 1: one tensor a token (a latent that serves as both), at half the memory.
+    `chunk`: queries see only the keys of their own run of `chunk` positions (runs counted from
+    position 0), so the pages of earlier runs are given back as the request moves on."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     planes: int = 2
+    chunk: int | None = None
 
 
 @dataclass(frozen=True)
@@ -83,6 +91,26 @@ class StateNeed:
     dtype: str = "float32"
 
 
+class PendingSum:
+    """Branch outputs that are not yet added to the residual: `terms`, a list of (tensor, scale), each
+    tensor float32 [N, W] or a K-split stack [P, N, W].  A block whose branches run side by side hands
+    one on as its `delta`; a norm that takes it adds every term in the kernel that norms the sum."""
+
+    __slots__ = ("terms",)
+
+    def __init__(self, terms=()):
+        self.terms = list(terms)
+
+    @staticmethod
+    def of(delta, scale: float = 1.0) -> list:
+        """The terms of a delta in any of its forms (None, a tensor, a PendingSum), each times `scale`."""
+        if delta is None:
+            return []
+        if isinstance(delta, PendingSum):
+            return [(tensor, s * scale) for tensor, s in delta.terms]
+        return [(delta, scale)]
+
+
 MIXERS: dict[str, type] = {}
 FEED_FORWARDS: dict[str, type] = {}
 NORMS: dict[str, type] = {}
@@ -90,10 +118,12 @@ POSITIONS: dict[str, type] = {}
 BLOCKS: dict[str, type] = {}
 EMBEDDINGS: dict[str, type] = {}
 HEADS: dict[str, type] = {}
+PASS_ENTRIES: dict[str, type] = {}
 
 _CATEGORIES = {
     "embedding": EMBEDDINGS,
     "head": HEADS,
+    "pass_entry": PASS_ENTRIES,
     "mixer": MIXERS,
     "feed_forward": FEED_FORWARDS,
     "norm": NORMS,
@@ -104,7 +134,7 @@ _CATEGORIES = {
 
 def register_part(category: str, kind: str, cls: type) -> type:
     """Adds a part class; `category` is one of mixer, feed_forward, norm, position, block,
-    embedding, head."""
+    embedding, head, pass_entry."""
     _CATEGORIES[category][kind] = cls
     return cls
 

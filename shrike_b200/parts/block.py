@@ -1,5 +1,9 @@
 """Residual blocks.
 
+`ParallelBlock`: both branches read the same residual, x += mixer(norm1(x)) + ff(norm2(x)).  The two
+norms come from one pass over the row where the norm part offers that (`add_norm_pair`), and the
+branch outputs stay pending (a `PendingSum`): the next norm kernel adds them, so the sum costs no pass.
+
 `BranchNormBlock`: the norm sits on a branch's OUTPUT, x += norm(mixer(x)); x += norm(ffn(x)), and both
 branches read x itself; the feed-forward may be absent.  The residual sum is 32-bit; a 16-bit engine
 gets the rounded residual a branch reads from the kernel that made the sum.
@@ -14,7 +18,7 @@ the same kernels with the same arguments in the same order, without the interpre
 
 from __future__ import annotations
 
-from .base import register_part
+from .base import PendingSum, register_part
 
 
 class PreNormBlock:
@@ -79,5 +83,32 @@ class BranchNormBlock:
         return resid, None
 
 
+class ParallelBlock:
+    capture_safe = True
+
+    def __init__(self, mixer, mixer_norm, feed_forward=None, feed_forward_norm=None):
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self.mixer = mixer
+        self.mixer_norm = mixer_norm
+        self.feed_forward = feed_forward
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(self, resid, delta, ctx, run):
+        if self.feed_forward is None:
+            hidden = self.mixer_norm.add_norm(resid, delta)
+            return resid, PendingSum(PendingSum.of(self.mixer.forward(hidden, ctx, run)))
+        pair = getattr(self.mixer_norm, "add_norm_pair", None)
+        if pair is not None:
+            for_mixer, for_ffn = pair(resid, delta, self.feed_forward_norm)
+        else:
+            for_mixer = self.mixer_norm.add_norm(resid, delta, "normed")
+            for_ffn = self.feed_forward_norm.add_norm(resid, None, "normed_b")
+        mixed = self.mixer.forward(for_mixer, ctx, run)
+        fed = self.feed_forward.forward(for_ffn, ctx)
+        return resid, PendingSum(PendingSum.of(mixed) + PendingSum.of(fed))
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "branch_norm", BranchNormBlock)

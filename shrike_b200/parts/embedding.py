@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import ParamSpec, register_part
+from .base import ParamSpec, PendingSum, register_part
 
 
 class TokenEmbedding:
@@ -29,8 +29,54 @@ class TokenEmbedding:
 
     def forward(self, ctx) -> torch.Tensor:
         resid = self.runtime.buffer("resid", (ctx.num_tokens, self.spec.width), torch.float32)
-        self.ops.embed(ctx.token_ids, self.table, resid, ctx.previous_tokens)
+        keep = ctx.carried.get("embedding_copy")   # a pass entry may ask for a second copy of what leaves here
+        scale = getattr(self.spec, "scale", 1.0)
+        if keep is None and scale == 1.0:
+            self.ops.embed(ctx.token_ids, self.table, resid, ctx.previous_tokens)
+        else:
+            self.ops.embed(ctx.token_ids, self.table, resid, ctx.previous_tokens, scale=scale, keep=keep)
+            if keep is not None:
+                ctx.carried["embedding_copied"] = True
         return resid
+
+
+class PassEntry:
+    """What entering pass t over a run of repeated layers does to the residual: the embedding's output is
+    added again (every pass but the first) and the learned vector step[t], in 32-bit, in the kernel that
+    also adds whatever branch outputs are still pending."""
+
+    capture_safe = True
+
+    @staticmethod
+    def parameters(spec) -> dict[str, ParamSpec]:
+        return {"step": ParamSpec((spec.passes, spec.width), "bias")}
+
+    def __init__(self, spec, tensors, ops, runtime):
+        self.spec, self.ops, self.runtime = spec, ops, runtime
+        self.step = tensors["step"].to(torch.float32).contiguous()
+        self._kept = None
+
+    def before_embedding(self, ctx) -> None:
+        self._kept = None
+        if self.spec.add_embedding and self.spec.passes > 1:
+            self._kept = self.runtime.buffer("embedding_out", (ctx.num_tokens, self.spec.width), torch.float32)
+            ctx.carried["embedding_copy"] = self._kept
+
+    def begin(self, resid, ctx) -> None:
+        if self._kept is not None and not ctx.carried.get("embedding_copied"):
+            self._kept.copy_(resid)   # an embedding part that does not write the copy itself
+
+    def forward(self, resid, delta, ctx, number: int):
+        if not 0 <= number < self.spec.passes:
+            raise ValueError(f"pass {number} of {self.spec.passes}")
+        terms = PendingSum.of(delta)
+        if number > 0 and self._kept is not None:
+            terms.append((self._kept, 1.0))
+        while len(terms) > 4:
+            self.ops.tanh_norm(resid, terms[:4])
+            terms = terms[4:]
+        self.ops.tanh_norm(resid, terms, row_add=self.step[number])
+        return resid, None
 
 
 class TokenPositionEmbedding:
@@ -76,3 +122,4 @@ class LMHead:
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "token_position_embedding", TokenPositionEmbedding)
 register_part("head", "lm_head", LMHead)
+register_part("pass_entry", "pass_entry", PassEntry)

@@ -11,7 +11,9 @@ import torch
 from .base import ParamSpec, register_part
 
 
-ACTIVATIONS = ("silu", "gelu_tanh")   # gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+# gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)));
+# clamped_swish with limit L: g <- min(g, L), u <- clamp(u, -L, L), then g sigmoid(1.702 g) (u + 1) in place of act(g) u
+ACTIVATIONS = ("silu", "gelu_tanh", "clamped_swish")
 
 
 class GatedMLP:
@@ -32,6 +34,9 @@ class GatedMLP:
         self.spec = spec
         self.ops = ops
         self.runtime = runtime
+        self.limit = getattr(spec, "limit", None)
+        if spec.activation == "clamped_swish" and (self.limit is None or not self.limit > 0):
+            raise ValueError("the clamped activation needs a positive limit")
         gate, up = tensors.pop("gate_proj.weight"), tensors.pop("up_proj.weight")
         run = getattr(ops, "gated_rows", 0)
         self.run = run if run and spec.intermediate % run == 0 else 0
@@ -47,10 +52,11 @@ class GatedMLP:
         spec, rt, ops = self.spec, self.runtime, self.ops
         n = x.shape[0]
         act = rt.buffer("ffn_act", (n, spec.intermediate), rt.act_dtype)
-        if not (self.run and ops.linear_gated(x, self.w_gate_up, act, spec.activation)):
+        extra = {} if self.limit is None else {"limit": self.limit}
+        if not (self.run and ops.linear_gated(x, self.w_gate_up, act, spec.activation, **extra)):
             gate_up = rt.buffer("gate_up", (n, 2 * spec.intermediate), rt.act_dtype)
             ops.linear(x, self.w_gate_up, gate_up)
-            ops.act_mul(gate_up, act, self.run, spec.activation)
+            ops.act_mul(gate_up, act, self.run, spec.activation, **extra)
         delta = rt.buffer("ffn_delta", (n, spec.width), torch.float32)
         return ops.linear(act, self.w_down, delta, allow_partials=True)
 

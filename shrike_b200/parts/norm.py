@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import ParamSpec, register_part
+from .base import ParamSpec, PendingSum, register_part
 
 
 class RMSNorm:
@@ -97,5 +97,61 @@ class LayerNorm:
         return out
 
 
+class DynamicTanh:
+    """tanh(alpha x) * weight + bias with one learned number alpha: a norm that takes no mean and no
+    variance, so it is elementwise and several of them can share one pass over a row.  The pending
+    branch outputs (a tensor, a K-split stack, or a `PendingSum` of several with a scale each) are
+    added to the float32 residual in the same kernel."""
+
+    capture_safe = True
+    MAX_TERMS = 4   # pending sums one launch of the kernel adds
+
+    @staticmethod
+    def parameters(spec) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((spec.width,), "norm"), "bias": ParamSpec((spec.width,), "bias"),
+                "alpha": ParamSpec((), "norm")}
+
+    def __init__(self, spec, tensors, ops, runtime):
+        self.spec, self.ops, self.runtime = spec, ops, runtime
+        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.bias = tensors["bias"].to(torch.float32).contiguous()
+        self.alpha = float(tensors["alpha"].to(torch.float32))   # a constant of the model, handed to the kernel by value
+
+    def _flush(self, resid, delta) -> list:
+        """The pending terms one launch can take; what is over is added to the residual first."""
+        terms = PendingSum.of(delta)
+        while len(terms) > self.MAX_TERMS:
+            self.ops.tanh_norm(resid, terms[: self.MAX_TERMS])
+            terms = terms[self.MAX_TERMS:]
+        return terms
+
+    def _triple(self, out):
+        return (self.alpha, self.weight, self.bias, out)
+
+    def add_norm(self, resid, delta, out_name="normed"):
+        out = self.runtime.buffer(out_name, (resid.shape[0], self.spec.width), self.runtime.act_dtype)
+        self.ops.tanh_norm(resid, self._flush(resid, delta), norms=[self._triple(out)])
+        return out
+
+    def add_norm_pair(self, resid, delta, other, out_names=("normed", "normed_b")):
+        """This norm and `other` (of the same kind) of the same summed row, from one pass over it."""
+        if not isinstance(other, DynamicTanh):
+            return self.add_norm(resid, delta, out_names[0]), other.add_norm(resid, None, out_names[1])
+        shape = (resid.shape[0], self.spec.width)
+        first = self.runtime.buffer(out_names[0], shape, self.runtime.act_dtype)
+        second = self.runtime.buffer(out_names[1], shape, self.runtime.act_dtype)
+        self.ops.tanh_norm(resid, self._flush(resid, delta), norms=[self._triple(first), other._triple(second)])
+        return first, second
+
+    def gather_norm(self, resid, delta, rows, out_name="normed_rows"):
+        out = self.runtime.buffer(out_name, (rows.shape[0], self.spec.width), self.runtime.act_dtype)
+        terms = PendingSum.of(delta)
+        if len(terms) > self.MAX_TERMS:
+            terms = self._flush(resid, delta)
+        self.ops.tanh_norm(resid, terms, rows=rows, norms=[self._triple(out)])
+        return out
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)
 register_part("norm", "layernorm", LayerNorm)

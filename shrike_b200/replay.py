@@ -39,7 +39,7 @@ from pathlib import Path
 import torch
 
 DEFAULT_PAGE_SIZE = 16
-DEFAULT_MAX_LIVE = 16
+DEFAULT_MAX_LIVE = 4
 
 
 def pages_for(max_tokens: int, page_size: int, max_live: int) -> int:

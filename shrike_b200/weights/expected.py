@@ -25,6 +25,10 @@ def expected_tensors(config: ModelConfig) -> dict[str, ParamSpec]:
         for role, category, spec in layer.roles():
             for local, param in part_class(category, spec.kind).parameters(spec).items():
                 table[names.layer_tensor(index, role, local)] = param
+    if config.pass_entry is not None:
+        entry = config.pass_entry
+        for local, param in part_class("pass_entry", entry.kind).parameters(entry).items():
+            table[names.pass_entry_name(local)] = param
     norm = config.final_norm
     for local, param in part_class("norm", norm.kind).parameters(norm).items():
         table[names.final_norm_name(local)] = param

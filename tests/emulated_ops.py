@@ -25,13 +25,116 @@ class EmulatedOps:
         if head_dim % 16 or not 16 <= head_dim <= 1024:
             raise ValueError(f"head size {head_dim} is not served")
 
-    def embed(self, ids, table, out, previous=None, position_table=None, positions=None):
+    def embed(self, ids, table, out, previous=None, position_table=None, positions=None, scale=1.0, keep=None):
         ids = ids.long()
         if previous is not None and (ids < 0).any():
             ids = torch.where(ids < 0, previous.long()[(-1 - ids).clamp(min=0, max=previous.numel() - 1)], ids)
-        out.copy_(table[ids].float())
+        out.copy_(table[ids].float() * scale)
         if position_table is not None:
             out.add_(position_table[positions.long()].float())
+        if keep is not None:
+            keep.copy_(out)
+
+    def tanh_norm(self, resid, terms=(), row_add=None, rows=None, norms=()):
+        x = resid if rows is None else resid[rows.long()]
+        for tensor, scale in terms:
+            summed = tensor.float().sum(0) if tensor.dim() == 3 else tensor.float()
+            x = x + scale * (summed if rows is None else summed[rows.long()])
+        if row_add is not None:
+            x = x + row_add
+        if rows is None and (terms or row_add is not None):
+            resid.copy_(x)
+        for alpha, weight, bias, out in norms:
+            out.copy_((torch.tanh(alpha * x) * weight + bias).to(out.dtype))
+
+    def head_prep(self, fused, bias, positions, inv_freq, rot, q_weight, k_weight, eps, q_out, keys, values, slots,
+                  gate_out, num_heads, num_kv_heads, dim, vdim, padded):
+        if fused.dim() == 3:
+            fused = fused.sum(0)
+        n = fused.shape[0]
+        x = fused.float() if bias is None else fused.float() + bias
+        q_cols, k_cols, v_cols = num_heads * dim, num_kv_heads * dim, num_kv_heads * vdim
+        q = x[:, :q_cols].view(n, num_heads, dim)
+        k = x[:, q_cols: q_cols + k_cols].view(n, num_kv_heads, dim)
+        v = x[:, q_cols + k_cols: q_cols + k_cols + v_cols].view(n, num_kv_heads, vdim)
+        if q_weight is not None:
+            q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+        if k_weight is not None:
+            k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        if inv_freq is not None and rot:
+            half = rot // 2
+            angle = positions.float()[:, None] * inv_freq[None, :]
+            cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+
+            def turn(t):
+                a, b = t[..., :half], t[..., half:rot]
+                return torch.cat([a * cos - b * sin, b * cos + a * sin, t[..., rot:]], -1)
+
+            q, k = turn(q), turn(k)
+
+        def pad(t, heads, size):
+            wide = torch.zeros(n, heads, padded)
+            wide[:, :, :size] = t
+            return wide.view(n, -1)
+
+        q_out.copy_(pad(q, num_heads, dim).to(q_out.dtype))
+        if gate_out is not None:
+            gate_out.copy_(torch.sigmoid(x[:, q_cols + k_cols + v_cols: q_cols + k_cols + v_cols + num_heads]))
+        if keys is not None:
+            stored = slots.long() >= 0
+            self.kv_write(pad(k, num_kv_heads, dim)[stored], pad(v, num_kv_heads, vdim)[stored], keys, values, slots[stored])
+
+    def matrix_memory(self, fused, gate_bias, state, q_start, state_slot, numerator, denominator, weight, eps, out,
+                      num_seqs, num_heads, dim, vdim, cap, floor):
+        if fused.dim() == 3:
+            fused = fused.sum(0)
+        x = fused.float()
+        H, D, Dv = num_heads, dim, vdim
+        out.zero_()
+        for s in range(num_seqs):
+            slot = int(state_slot[s])
+            if slot < 0:
+                continue
+            held = state[slot]
+            S = held[:, : D * Dv].reshape(H, D, Dv).clone()
+            z = held[:, D * Dv: D * Dv + D].clone()
+            m = held[:, D * Dv + D].clone()
+            for t in range(int(q_start[s]), int(q_start[s + 1])):
+                row = x[t]
+                q = row[: H * D].view(H, D) * D ** -0.5
+                k = row[H * D: 2 * H * D].view(H, D)
+                v = row[2 * H * D: 2 * H * D + H * Dv].view(H, Dv)
+                g = row[2 * H * D + H * Dv: 2 * H * D + 2 * H * Dv]
+                gates = row[2 * H * D + 2 * H * Dv: 2 * H * D + 2 * H * Dv + 2 * H] + gate_bias
+                a = cap * torch.tanh(gates[:H] / cap)
+                f = torch.nn.functional.logsigmoid(cap * torch.tanh(gates[H:] / cap))
+                m_new = torch.maximum(f + m, a)
+                keep, take = torch.exp(f + m - m_new), torch.exp(a - m_new)
+                S = keep[:, None, None] * S + take[:, None, None] * k[:, :, None] * v[:, None, :]
+                z = keep[:, None] * z + take[:, None] * k
+                m = m_new
+                o = torch.einsum("hdv,hd->hv", S, q) / (torch.maximum((z * q).sum(-1).abs(), torch.exp(-m)) + floor)[:, None]
+                o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+                out[t] = (o.reshape(-1) * weight * torch.sigmoid(g)).to(out.dtype)
+            held[:, : D * Dv] = S.reshape(H, -1)
+            held[:, D * Dv: D * Dv + D] = z
+            held[:, D * Dv + D] = m
+
+    def route_top(self, x, router, shared_gate, weights, top, renorm_eps):
+        scores = torch.softmax(x.float() @ router.T, -1)
+        best, chosen = torch.topk(scores, top, -1)
+        weights.zero_()
+        weights[:, : router.shape[0]].scatter_(1, chosen, best / (best.sum(-1, keepdim=True) + renorm_eps))
+        if weights.shape[1] > router.shape[0]:
+            weights[:, -1] = 1.0 if shared_gate is None else torch.sigmoid(x.float() @ shared_gate)
+
+    def act_mul_blocks(self, gate_up, weights, out, experts, each, activation="silu", limit=None):
+        inter = out.shape[1]
+        column = torch.arange(inter)
+        block = torch.where(column < experts * each, column // each, torch.full_like(column, experts))
+        plain = torch.empty(out.shape, dtype=torch.float32)
+        self.act_mul(gate_up, plain, 0, activation, limit)
+        out.copy_((plain * weights[:, block]).to(out.dtype))
 
     @staticmethod
     def _norm(x, weight, bias, eps, layer_norm):
@@ -156,7 +259,7 @@ class EmulatedOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None):
+                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None, chunk=None):
         page = keys.shape[1]
         group = num_heads // num_kv_heads
         n = q.shape[0]
@@ -166,6 +269,8 @@ class EmulatedOps:
             q_len = int(q_start[s + 1]) - int(q_start[s])
             last = int(ctx_len[s]) - q_len + t
             first = 0 if not window else max(0, last - window + 1)
+            if chunk:
+                first = last // chunk * chunk
             idx = torch.arange(first, last + 1)
             pages = block_table[s].long()[idx // page]
             assert (pages >= 0).all(), "attention read a page that was given back"
@@ -184,12 +289,15 @@ class EmulatedOps:
     def silu_mul(self, gate_up, out):
         self.act_mul(gate_up, out)
 
-    def act_mul(self, gate_up, out, block=0, activation="silu"):
+    def act_mul(self, gate_up, out, block=0, activation="silu", limit=None):
         assert block == 0
         inter = out.shape[1]
         g = gate_up[:, :inter].float()
         u = gate_up[:, inter:].float()
-        if activation == "gelu_tanh":
+        if activation == "clamped_swish":
+            g = g.clamp(max=limit)
+            act, u = g * torch.sigmoid(1.702 * g), u.clamp(-limit, limit) + 1.0
+        elif activation == "gelu_tanh":
             act = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
         else:
             act = g * torch.sigmoid(g)
