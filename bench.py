@@ -475,11 +475,12 @@ def run_mixed(args) -> dict:
     from shrike_b200.weights.random_init import random_tensors
 
     torch.cuda.set_device(0)
-    sadodra = getattr(args, "arch", "qwen2") == "sadodra"   # the same workload on the Sadodra decoder at the same widths
+    design = getattr(args, "arch", "qwen2")   # the same workload on another decoder at the same widths
+    sadodra = design in ("sadodra", "vupitar")
     if sadodra:
         from shrike_b200.shapes import shape_config
 
-        raw = dict(shape_config("sadodra-1.5b"))
+        raw = dict(shape_config(f"{design}-1.5b"))
         if args.layers:
             raw["layers"] = raw["layers"][: args.layers]
         raw["vocab_size"], raw["num_hidden_layers"] = raw["vocab"], len(raw["layers"])
@@ -507,7 +508,7 @@ def run_mixed(args) -> dict:
     generated = sum(len(r) for r in results)
     assert [len(r) for r in results] == outputs and engine.block_manager.whole()
     return {
-        "workload": "mixed", "model": "Sadodra at Qwen2.5-1.5B widths" if sadodra else "Qwen2.5-1.5B shape",
+        "workload": "mixed", "model": f"{design.capitalize()} at Qwen2.5-1.5B widths" if sadodra else "Qwen2.5-1.5B shape",
         "layers": raw["num_hidden_layers"], "requests": 64,
         "prompt_tokens": sum(len(p) for p in prompts), "generated_tokens": generated, "seconds": round(seconds, 3),
         "value": round(generated / seconds, 1), "unit": "generated tok/s",
@@ -816,7 +817,7 @@ def run_design(args) -> dict:
         weight_bytes = engine.runner.model.weight_bytes()
         cache_bytes = runner.bytes_per_page / BLOCK_SIZE
         result = {
-            "model": name, "layers": config.num_layers, "weights_GB": round(weight_bytes / 1e9, 2),
+            "model": name, "layers": len(config.order), "weights_GB": round(weight_bytes / 1e9, 2),
             "cache_bytes_per_token": int(cache_bytes),
             "prefill": {"tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3), "tok_s": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1),
                         "kernels": prefill_kernels},
@@ -834,18 +835,23 @@ def run_design(args) -> dict:
         torch.cuda.empty_cache()
         return result
 
-    ours = dict(shape_config(f"sadodra-{args.design}"))
+    design = args.arch if args.arch != "qwen2" else "sadodra"
+    ours = dict(shape_config(f"{design}-{args.design}"))
     theirs = dict(shape_config(f"qwen2.5-{args.design}"))
     if args.layers:
-        ours["layers"] = ours["layers"][: args.layers]
-        theirs["num_hidden_layers"] = args.layers
+        # both models run `--layers` layers: a design that repeats some of its layers keeps its passes and
+        # gives up distinct layers (never fewer than the repeated stretch)
+        loop = ours.get("loop")
+        extra = (loop["stop"] - loop["start"]) * (loop["times"] - 1) if loop else 0
+        ours["layers"] = ours["layers"][: max(args.layers - extra, loop["stop"] if loop else 1)]
+        theirs["num_hidden_layers"] = len(parse_config(ours).order)
     sampler = ClockSampler()
     sampler.start()
     t0 = time.perf_counter()
-    results = [measure(f"Sadodra at Qwen2.5-{args.design.upper()} widths", ours),
+    results = [measure(f"{design.capitalize()} at Qwen2.5-{args.design.upper()} widths", ours),
                measure(f"Qwen2.5-{args.design.upper()} shape", theirs)]
     sampler.stop()
-    return {"case": "design", "design": "Sadodra", "closest": "Qwen2ForCausalLM", "dtype": "bf16",
+    return {"case": "design", "design": design.capitalize(), "closest": "Qwen2ForCausalLM", "dtype": "bf16",
             "data": "synthetic: seeded random weights and uniform random token ids", "peaks": peaks,
             "models": results, "clocks": sampler.summary([(t0, time.perf_counter())])}
 
@@ -873,8 +879,9 @@ def main():
     parser.add_argument("--context", type=int, default=1024, help="tokens each sequence holds when decoding is timed")
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")
-    parser.add_argument("--arch", default="qwen2", choices=["qwen2", "sadodra"],
-                        help="--workload mixed: the decoder the 64 requests run on (both at Qwen2.5-1.5B widths)")
+    parser.add_argument("--arch", default="qwen2", choices=["qwen2", "sadodra", "vupitar"],
+                        help="--workload mixed: the decoder the 64 requests run on (all at Qwen2.5-1.5B widths); "
+                             "--case design: the design that is set beside the Qwen2 decoder (default there: sadodra)")
     parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")
     parser.add_argument("--skip-mixed", action="store_true", help="leave the mixed workload out of the default line")
     parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,

@@ -204,9 +204,18 @@ __global__ void matrix_memory_scan_kernel(const ScanArgs a) {
   wait_for_previous();
   const int seq = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * a.cols;
   const int slot = a.state_slot[seq];
-  if (slot < 0 || slot >= a.num_slots) return;
   const int start = a.q_start[seq], count = a.q_start[seq + 1] - start;
   const int cols_here = min(a.cols, a.vdim - col0);
+  if (slot < 0 || slot >= a.num_slots) {
+    // a padding row of the batch: no state is touched; its outputs are made finite (0 over 1) for the kernels after
+    for (int idx = threadIdx.x; idx < count * cols_here; idx += blockDim.x) {
+      const int t = idx / cols_here, c = idx - t * cols_here;
+      a.numerator[(static_cast<size_t>(start + t) * a.heads + head) * a.vdim + col0 + c] = 0.f;
+    }
+    if (blockIdx.x == 0)
+      for (int t = threadIdx.x; t < count; t += blockDim.x) a.denominator[static_cast<size_t>(start + t) * a.heads + head] = 1.f;
+    return;
+  }
   const bool keeps_z = blockIdx.x == 0;
   const int ld = a.cols + 1;
   const int D = a.dim, Dv = a.vdim, H = a.heads;

@@ -102,7 +102,7 @@ def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor], metada
         if tensor.dtype not in _NAMES:
             raise SafetensorsError(f"tensor {name!r}: dtype {tensor.dtype} cannot be stored")
         data = tensor.detach().cpu().contiguous()
-        raw = data.view(torch.uint8).numpy().tobytes() if data.numel() else b""
+        raw = data.reshape(-1).view(torch.uint8).numpy().tobytes() if data.numel() else b""   # reshape: a scalar has no axis to view
         header[name] = {
             "dtype": _NAMES[tensor.dtype],
             "shape": list(tensor.shape),

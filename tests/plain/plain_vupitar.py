@@ -71,6 +71,22 @@ def chunk_mask(n: int, size: int) -> torch.Tensor:
     return (j <= i) & (torch.div(i, size, rounding_mode="floor") == torch.div(j, size, rounding_mode="floor"))
 
 
+def attend(q, k, v, scale, chunk=None, first_position=0) -> torch.Tensor:
+    """Softmax attention of queries q [m, H, D] at positions first_position .. over keys k [n, G, D] and
+    values v [n, G, Dv] at positions 0 .. n - 1 (n = first_position + m): head h uses key/value head
+    h // (H / G); query i sees key j <= i, and with `chunk` only if floor(i / chunk) = floor(j / chunk)."""
+    m, H, _ = q.shape
+    n, G = k.shape[0], k.shape[1]
+    seen = chunk_mask(n, chunk) if chunk else (torch.arange(n)[None, :] <= torch.arange(n)[:, None])
+    seen = seen[first_position:]
+    out = torch.empty(m, H, v.shape[-1], dtype=q.dtype)
+    for head in range(H):
+        g = head // (H // G)
+        s = (q[:, head] @ k[:, g].T) * scale
+        out[:, head] = torch.softmax(s.masked_fill(~seen, float("-inf")), dim=-1) @ v[:, g]
+    return out
+
+
 def chunked_attention(h, weights, prefix, spec, eps, rounding) -> torch.Tensor:
     n, dtype = h.shape[0], h.dtype
     H, G, D, Dv = spec["heads"], spec["kv_heads"], spec["dim"], spec["vdim"]
@@ -86,13 +102,7 @@ def chunked_attention(h, weights, prefix, spec, eps, rounding) -> torch.Tensor:
         q = rotate_partial(q, positions, rot["dims"], rot["base"])
         k = rotate_partial(k, positions, rot["dims"], rot["base"])
     q, k = _r(q, rounding), _r(k, rounding)
-    seen = chunk_mask(n, spec["mask"]["size"]) if spec.get("mask") else (torch.arange(n)[None, :] <= torch.arange(n)[:, None])
-    out = torch.empty(n, H, Dv, dtype=dtype)
-    for head in range(H):
-        g = head // (H // G)
-        s = (q[:, head] @ k[:, g].T) * spec["scale"]
-        s = s.masked_fill(~seen, float("-inf"))
-        out[:, head] = torch.softmax(s, dim=-1) @ v[:, g]
+    out = attend(q, k, v, spec["scale"], spec["mask"]["size"] if spec.get("mask") else None)
     gate = torch.sigmoid(h @ w("g").T)                          # [n, H]
     out = _r(out * gate[:, :, None], rounding).reshape(n, H * Dv)
     return out @ w("o").T + w("o.b")
@@ -154,16 +164,21 @@ def expert(h, weights, prefix, rounding) -> torch.Tensor:
     return _r(g * torch.sigmoid(g) * u, rounding) @ w("down").T
 
 
-def route(h, weights, prefix, experts: int, top: int):
-    """(chosen [n, top], weights [n, top]): softmax over all experts, the largest `top`, renormalised."""
+def route(h, weights, prefix, experts: int, top: int, gaps=None):
+    """(chosen [n, top], weights [n, top]): softmax over all experts, the largest `top`, renormalised.
+    `gaps`, a list, receives per token the gap of the logarithms of the scores (that is, of the router's logits)
+    between the last expert chosen and the first one left out."""
     scores = torch.softmax(h @ weights[f"{prefix}.router"].to(h.dtype).T, dim=-1)
     best, chosen = torch.topk(scores, top, dim=-1)
+    if gaps is not None and top < experts:
+        ranked = torch.sort(scores, dim=-1, descending=True).values
+        gaps.append(torch.log(ranked[:, top - 1]) - torch.log(ranked[:, top]))
     return chosen, best / (best.sum(-1, keepdim=True) + 1e-20)
 
 
-def expert_ff(h, weights, prefix, spec, rounding) -> torch.Tensor:
+def expert_ff(h, weights, prefix, spec, rounding, gaps=None) -> torch.Tensor:
     n = h.shape[0]
-    chosen, share = route(h, weights, prefix, spec["router"]["experts"], spec["router"]["top"])
+    chosen, share = route(h, weights, prefix, spec["router"]["experts"], spec["router"]["top"], gaps)
     out = torch.zeros(n, weights[f"{prefix}.e0.down"].shape[0], dtype=h.dtype)
     for e in range(spec["router"]["experts"]):
         rows, place = (chosen == e).nonzero(as_tuple=True)
@@ -175,21 +190,21 @@ def expert_ff(h, weights, prefix, spec, rounding) -> torch.Tensor:
     return out
 
 
-def feed_forward(h, weights, prefix, spec, rounding) -> torch.Tensor:
+def feed_forward(h, weights, prefix, spec, rounding, gaps=None) -> torch.Tensor:
     if spec["kind"] == "dense":
         return dense_ff(h, weights, prefix, spec, rounding)
     if spec["kind"] == "moe":
-        return expert_ff(h, weights, prefix, spec, rounding)
+        return expert_ff(h, weights, prefix, spec, rounding, gaps)
     raise ValueError(spec["kind"])
 
 
-def layer(x, weights, index: int, spec, eps, rounding) -> torch.Tensor:
+def layer(x, weights, index: int, spec, eps, rounding, gaps=None) -> torch.Tensor:
     name = f"l{index}"
     if spec["type"] != "parallel":
         raise ValueError(spec["type"])
     branch = parallel_mixer(_r(tanh_norm(x, weights, name + ".norm1"), rounding), weights, name + ".mix", spec["mixer"], eps, rounding)
     if spec.get("mlp") is not None:
-        branch = branch + feed_forward(_r(tanh_norm(x, weights, name + ".norm2"), rounding), weights, name + ".mlp", spec["mlp"], rounding)
+        branch = branch + feed_forward(_r(tanh_norm(x, weights, name + ".norm2"), rounding), weights, name + ".mlp", spec["mlp"], rounding, gaps)
     return x + branch
 
 
@@ -206,8 +221,9 @@ def run_order(raw: dict):
     return order + [(i, None) for i in range(loop["stop"], count)]
 
 
-def forward(raw: dict, weights: dict, tokens, dtype=torch.float64, rounding: bool = False, layers_out=None) -> torch.Tensor:
-    """Logits [n, vocab] of one whole sequence.  `layers_out`, a list, receives the residual after every run."""
+def forward(raw: dict, weights: dict, tokens, dtype=torch.float64, rounding: bool = False, layers_out=None, gaps=None) -> torch.Tensor:
+    """Logits [n, vocab] of one whole sequence.  `layers_out`, a list, receives the residual after every run;
+    `gaps`, a list, per routed layer run the router's margin at every token (see `route`)."""
     eps = raw["norm"]["eps"]
     ids = torch.as_tensor(tokens, dtype=torch.long)
     e = weights["embed"].to(dtype)[ids] * raw["embedding"]["scale"]
@@ -217,7 +233,19 @@ def forward(raw: dict, weights: dict, tokens, dtype=torch.float64, rounding: boo
             if opens > 0:
                 x = x + e
             x = x + weights["loop.step"].to(dtype)[opens]
-        x = layer(x, weights, index, raw["layers"][index], eps, rounding)
+        x = layer(x, weights, index, raw["layers"][index], eps, rounding, gaps)
         if layers_out is not None:
             layers_out.append(x.clone())
     return _r(tanh_norm(x, weights, "final.norm"), rounding) @ weights["head"].to(dtype).T
+
+
+def greedy_continue(raw: dict, weights: dict, prompt, count: int, dtype=torch.float64):
+    """`count` greedy tokens after `prompt`, each from a whole-sequence pass, and the gap between
+    the two largest logits at each step."""
+    tokens, margins = list(prompt), []
+    for _ in range(count):
+        logits = forward(raw, weights, tokens, dtype=dtype)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        tokens.append(int(torch.argmax(logits)))
+    return tokens[len(prompt):], margins
