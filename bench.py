@@ -575,6 +575,71 @@ def run_case(args) -> dict:
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3)
         work = {"bytes": rows * h * (4 + 4 + 4 + 2)}
+    elif args.case == "tanh_norm":
+        # resid += three pending branch outputs, then two tanh norms of the sum, rows of 7B width (--batch rows)
+        rows = tokens
+        resid = torch.randn(rows, h, device=dev, dtype=torch.float32)
+        pending = [(torch.randn(rows, h, device=dev, dtype=torch.float32), scale) for scale in (0.8, 1.1, 1.0)]
+        weight, bias = torch.ones(h, device=dev), torch.zeros(h, device=dev)
+        outs = [torch.empty(rows, h, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.tanh_norm(resid, pending, norms=[(0.5, weight, bias, outs[0]), (0.7, weight, bias, outs[1])])
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        work = {"bytes": rows * h * (4 + 3 * 4 + 4 + 2 + 2)}
+    elif args.case == "head_prep":
+        # q|k|v|gate of 7B heads from the fused product's float32 result: per-head norms, rotation, pages (--batch tokens)
+        total = -(-((heads + 2 * kv) * d + heads) // 16) * 16
+        fused = torch.randn(tokens, total, device=dev, dtype=torch.float32)
+        bias = torch.zeros(total, device=dev)
+        positions = torch.arange(tokens, dtype=torch.int32, device=dev)
+        inv_freq = torch.tensor([1e6 ** (-2.0 * i / d) for i in range(d // 2)], device=dev)
+        weight = torch.ones(d, device=dev)
+        q = torch.empty(tokens, heads * d, device=dev, dtype=torch.bfloat16)
+        pages = -(-tokens // BLOCK_SIZE)
+        keys = torch.empty(pages, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16)
+        values = torch.empty_like(keys)
+        gate = torch.empty(tokens, heads, device=dev)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.head_prep(fused, bias, positions, inv_freq, d, weight, weight, 1e-6, q, keys, values, positions, gate, heads, kv, d, d, d)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        work = {"bytes": tokens * (total * 4 + (heads + 2 * kv) * d * 2 + heads * 4)}
+    elif args.case in ("matrix_memory", "matrix_memory_single"):
+        # the matrix memory of the 7B-width shape (8 heads of 128 x 256): one prompt of --prefill-tokens tokens (chunk
+        # kernels), or --batch sequences one token each (the walk)
+        mh, md, mv = 8, 128, 256
+        single = args.case.endswith("_single")
+        seqs, q_len = (tokens, 1) if single else (1, args.prefill_tokens)
+        n = seqs * q_len
+        total = -(-(2 * mh * md + 2 * mh * mv + 2 * mh) // 16) * 16
+        fused = torch.randn(n, total, device=dev, dtype=torch.float32) * 0.3
+        gate_bias = torch.zeros(2 * mh, device=dev)
+        state = torch.zeros(seqs, mh, md * mv + md + 4, device=dev)
+        q_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        num, den = torch.empty(n, mh * mv, device=dev), torch.empty(n, mh, device=dev)
+        out = torch.empty(n, mh * mv, device=dev, dtype=torch.bfloat16)
+        weight = torch.ones(mh * mv, device=dev)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.matrix_memory(fused, gate_bias, state, q_start, slots, num, den, weight, 1e-6, out, seqs, mh, md, mv, 15.0, 1e-6,
+                              longest=q_len)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        chunks = -(-q_len // 64)
+        # per head and chunk: scores 64 x 64 x dim, their outputs 64 x 64 x vdim, the state's addition and the state's
+        # part of the outputs 2 x 64 x dim x vdim (2 flops a multiply-add)
+        work = {"bytes": seqs * mh * (md * mv + md) * 4 * 2 + n * total * 4} if single else \
+               {"flops": 2.0 * seqs * mh * chunks * (64 * 64 * md + 64 * 64 * mv + 2 * 64 * md * mv)}
     elif args.case in ("attention_single", "attention_portions", "attention_single_scores", "attention_portions_scores",
                        "attention_single_latent", "attention_portions_latent"):
         single = args.case.startswith("attention_single")
@@ -714,7 +779,7 @@ def run_timeline(args) -> dict:
 
 
 def run_design(args) -> dict:
-    """The Sadodra decoder beside the Qwen2 decoder of the same widths, layer count and vocabulary (the
+    """A design (--arch sadodra, the default here, or vupitar) beside the Qwen2 decoder of the same widths, layer count and vocabulary (the
     closest model this engine serves), random weights: one 2,048-token prompt in one step, and decoding
     at --batch sequences of --context tokens, device-timed through the step function and the sampling
     kernel; for each, the kernels of one step by the time they take (CUPTI activity records).
@@ -892,7 +957,8 @@ def main():
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
                              "gemm_qkv, attention_single, attention_portions (with _scores: soft-capped and distance-biased; with _latent: "
                              "one key/value head of 256 whose keys are its values), "
-                             "branch_norm; --batch gives tokens / sequences / rows.  timeline: per-kernel "
+                             "branch_norm, tanh_norm, head_prep, matrix_memory (a prompt of --prefill-tokens), matrix_memory_single; "
+                             "--batch gives tokens / sequences / rows.  timeline: per-kernel "
                              "times inside one captured decode step (--layers, default 6).  design: the Sadodra decoder "
                              "beside the Qwen2 decoder of equal widths (--design), prefill and decode")
     args = parser.parse_args()

@@ -54,13 +54,10 @@ class CacheStorage:
         }
 
     def zero_slots(self, slots: list[int]) -> None:
-        """Zeroes the state of `slots` in every stateful cache (one indexed fill each)."""
+        """Zeroes the state of `slots` in every stateful cache: one launch for all of them."""
         if not slots or not self.state:
             return
-        first = next(iter(self.state.values()))
-        index = torch.tensor(slots, dtype=torch.long, device=first.device)
-        for tensor in self.state.values():
-            tensor.index_fill_(0, index, 0)
+        torch._foreach_zero_([tensor[slot] for tensor in self.state.values() for slot in slots])
 
     def keys_values(self, cache_id: int):
         """(group index, keys, values), each `[pages, page_size, kv heads, head size]`; in a group of one

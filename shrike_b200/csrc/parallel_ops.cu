@@ -9,6 +9,8 @@
 //                      (heads padded to the kernels' head size), sigmoid of the per-head gate
 //   matrix_memory_scan the recurrence S_t = keep_t S_(t-1) + take_t k_t v_t^T of a matrix-memory mixer, token by
 //                      token with the state on chip, for portions and single tokens alike
+//   matrix_memory_scores / _local / _carry / _finish   the same for portions, as products over chunks of 64 tokens, every
+//                      chunk on a CTA of its own
 //   matrix_memory_out  its outputs: divided by their denominator, each head over its root mean square, times a
 //                      weight and a sigmoid gate
 //   route_top          router logits, softmax over all experts, the `top` largest renormalised, as a dense
@@ -65,27 +67,54 @@ __global__ void __launch_bounds__(256) tanh_norm_kernel(const TanhNormArgs a) {
     for (int group = blockIdx.x * blockDim.x + threadIdx.x; group < groups; group += gridDim.x * blockDim.x) {
       const int col = group * VEC;
       float x[VEC];
+      if constexpr (VEC == 4) {
+        load4<float>(a.resid + src_base + col, x);
+        for (int t = 0; t < a.num_terms; ++t) {
+          const SumTerm& term = a.terms[t];
+          float part[4];
+          sum_partials4(term.data + src_base + col, term.stride, term.partials, part);
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) x[e] = a.resid[src_base + col + e];
-      for (int t = 0; t < a.num_terms; ++t) {
-        const SumTerm& term = a.terms[t];
+          for (int e = 0; e < 4; ++e) x[e] = __fmaf_rn(term.scale, part[e], x[e]);
+        }
+        if (a.row_add != nullptr) {
+          float part[4];
+          load4<float>(a.row_add + col, part);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e)
-          x[e] = __fmaf_rn(term.scale, sum_partials(term.data + src_base + col + e, term.stride, term.partials), x[e]);
-      }
-      if (a.row_add != nullptr) {
+          for (int e = 0; e < 4; ++e) x[e] = __fadd_rn(x[e], part[e]);
+        }
+        if (a.rows == nullptr && (a.num_terms > 0 || a.row_add != nullptr)) store4<float>(a.resid + src_base + col, x);
+      } else {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) x[e] = __fadd_rn(x[e], a.row_add[col + e]);
-      }
-      if (a.rows == nullptr && (a.num_terms > 0 || a.row_add != nullptr)) {
+        for (int e = 0; e < VEC; ++e) x[e] = a.resid[src_base + col + e];
+        for (int t = 0; t < a.num_terms; ++t) {
+          const SumTerm& term = a.terms[t];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) a.resid[src_base + col + e] = x[e];
+          for (int e = 0; e < VEC; ++e)
+            x[e] = __fmaf_rn(term.scale, sum_partials(term.data + src_base + col + e, term.stride, term.partials), x[e]);
+        }
+        if (a.row_add != nullptr) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) x[e] = __fadd_rn(x[e], a.row_add[col + e]);
+        }
+        if (a.rows == nullptr && (a.num_terms > 0 || a.row_add != nullptr)) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) a.resid[src_base + col + e] = x[e];
+        }
       }
       for (int k = 0; k < a.norms; ++k) {
         TO* out = static_cast<TO*>(a.out[k]) + out_base + col;
+        if constexpr (VEC == 4) {
+          float w[4], b[4], y[4];
+          load4<float>(a.weight[k] + col, w);
+          load4<float>(a.bias[k] + col, b);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e)
-          out[e] = from_float<TO>(__fmaf_rn(tanh_for<TO>(a.alpha[k] * x[e]), a.weight[k][col + e], a.bias[k][col + e]));
+          for (int e = 0; e < 4; ++e) y[e] = __fmaf_rn(tanh_for<TO>(a.alpha[k] * x[e]), w[e], b[e]);
+          store4<TO>(out, y);
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            out[e] = from_float<TO>(__fmaf_rn(tanh_for<TO>(a.alpha[k] * x[e]), a.weight[k][col + e], a.bias[k][col + e]));
+        }
       }
     }
   }
@@ -114,16 +143,8 @@ struct HeadPrepArgs {
 constexpr int PREP_WARPS = 4;
 
 template <typename T>
-__global__ void __launch_bounds__(PREP_WARPS * 32) head_prep_kernel(const HeadPrepArgs a) {
-  extern __shared__ float prep_shared[];
-  let_dependents_start();
-  wait_for_previous();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int units = a.heads + 2 * a.kv_heads + (a.gate_out != nullptr ? 1 : 0);
-  const long long work = static_cast<long long>(blockIdx.x) * PREP_WARPS + warp;
-  if (work >= static_cast<long long>(a.n) * units) return;
-  const int token = static_cast<int>(work / units), unit = static_cast<int>(work - static_cast<long long>(token) * units);
-  const float* row = a.fused + static_cast<size_t>(token) * a.total;
+__device__ __forceinline__ void head_prep_unit(const HeadPrepArgs& a, const float* row, int token, int unit, float* mine,
+                                               const float* cosines, const float* sines, int lane) {
   const int q_cols = a.heads * a.dim, k_cols = a.kv_heads * a.dim, v_cols = a.kv_heads * a.vdim;
   if (unit == a.heads + 2 * a.kv_heads) {   // the gates: one number a head
     for (int h = lane; h < a.heads; h += 32) {
@@ -145,32 +166,102 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) head_prep_kernel(const HeadPr
     if (a.keys == nullptr || slot < 0 || slot >= a.num_slots) return;
     dst = static_cast<T*>(is_k ? a.keys : a.values) + (static_cast<size_t>(slot) * a.kv_heads + head) * a.padded;
   }
-  float* mine = prep_shared + static_cast<size_t>(warp) * a.padded;
+  const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
+  const int half = (is_q || is_k) && a.inv_freq != nullptr ? a.rot / 2 : 0;
+  // four consecutive elements a lane, 16-byte accesses, where sizes and addresses allow
+  const bool wide = (size & 3) == 0 && (a.padded & 3) == 0 && (first_col & 3) == 0 && (a.total & 3) == 0 && (a.stride & 3) == 0 &&
+                    (half & 3) == 0 && (reinterpret_cast<uintptr_t>(a.fused) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
   float squares = 0.f;
+  if (wide) {
+    for (int d = lane * 4; d < size; d += 128) {
+      float v[4];
+      sum_partials4(row + first_col + d, a.stride, a.partials, v);
+      if (a.bias != nullptr) {
+        float b[4];
+        load4<float>(a.bias + first_col + d, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = __fadd_rn(v[e], b[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        mine[d + e] = v[e];
+        squares = __fmaf_rn(v[e], v[e], squares);
+      }
+    }
+    if (weight != nullptr) {
+      const float r = rsqrtf(warp_sum(squares) / static_cast<float>(size) + a.eps);
+      for (int d = lane * 4; d < size; d += 128) {
+        float w[4];
+        load4<float>(weight + d, w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mine[d + e] = mine[d + e] * r * w[e];
+      }
+    }
+    __syncwarp();
+    for (int d = lane * 4; d < a.padded; d += 128) {
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int at = d + e;
+        v[e] = at < size ? mine[at] : 0.f;
+        if (at < 2 * half) {
+          const int i = at < half ? at : at - half;
+          const float sine = sines[i], cosine = cosines[i];
+          const float u = mine[i], w = mine[i + half];
+          v[e] = at < half ? __fsub_rn(__fmul_rn(u, cosine), __fmul_rn(w, sine)) : __fadd_rn(__fmul_rn(w, cosine), __fmul_rn(u, sine));
+        }
+      }
+      store4<T>(dst + d, v);
+    }
+    return;
+  }
   for (int d = lane; d < size; d += 32) {
     float v = sum_partials(row + first_col + d, a.stride, a.partials);
     if (a.bias != nullptr) v = __fadd_rn(v, a.bias[first_col + d]);
     mine[d] = v;
     squares = __fmaf_rn(v, v, squares);
   }
-  const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
   if (weight != nullptr) {
     const float r = rsqrtf(warp_sum(squares) / static_cast<float>(size) + a.eps);
     for (int d = lane; d < size; d += 32) mine[d] = mine[d] * r * weight[d];
   }
   __syncwarp();
-  const int half = (is_q || is_k) && a.inv_freq != nullptr ? a.rot / 2 : 0;
-  const float position = static_cast<float>(a.positions[token]);
   for (int d = lane; d < a.padded; d += 32) {
     float v = d < size ? mine[d] : 0.f;
     if (d < 2 * half) {
       const int i = d < half ? d : d - half;
-      float sine, cosine;
-      sincosf(__fmul_rn(position, a.inv_freq[i]), &sine, &cosine);
+      const float sine = sines[i], cosine = cosines[i];
       const float u = mine[i], w = mine[i + half];
       v = d < half ? __fsub_rn(__fmul_rn(u, cosine), __fmul_rn(w, sine)) : __fadd_rn(__fmul_rn(w, cosine), __fmul_rn(u, sine));
     }
     dst[d] = from_float<T>(v);
+  }
+}
+
+// A block serves one token's units (query heads, key heads, value heads, the gates) numbered blockIdx.y, blockIdx.y +
+// gridDim.y, ...: few tokens are spread over many blocks, many tokens get one block each.  The rotation's sines and
+// cosines depend on the token alone: the block forms them once and every head uses them.
+template <typename T>
+__global__ void __launch_bounds__(PREP_WARPS * 32) head_prep_kernel(const HeadPrepArgs a) {
+  extern __shared__ float prep_shared[];   // [PREP_WARPS][padded] a warp's head, then [rot / 2] cosines and sines
+  let_dependents_start();
+  wait_for_previous();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int units = a.heads + 2 * a.kv_heads + (a.gate_out != nullptr ? 1 : 0);
+  const int token = blockIdx.x;
+  const float* row = a.fused + static_cast<size_t>(token) * a.total;
+  const int table_half = a.inv_freq != nullptr ? a.rot / 2 : 0;
+  float* cosines = prep_shared + static_cast<size_t>(PREP_WARPS) * a.padded;
+  float* sines = cosines + table_half;
+  const float position = static_cast<float>(a.positions[token]);
+  for (int i = threadIdx.x; i < table_half; i += blockDim.x) sincosf(__fmul_rn(position, a.inv_freq[i]), &sines[i], &cosines[i]);
+  __syncthreads();
+  float* mine = prep_shared + static_cast<size_t>(warp) * a.padded;
+  for (int unit = blockIdx.y * PREP_WARPS + warp; unit < units; unit += gridDim.y * PREP_WARPS) {
+    head_prep_unit<T>(a, row, token, unit, mine, cosines, sines, lane);
+    __syncwarp();   // the warp's buffer is read across lanes until a head is stored
   }
 }
 
@@ -179,22 +270,59 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) head_prep_kernel(const HeadPr
 // order.  Thread j holds column j: S[:, j] lives in shared memory as S[d * ld + j].  The normaliser z (the
 // recurrence with v = 1) is one more column, kept by the CTA of the head's first columns.  Tokens are staged
 // TOKENS at a time (q, k, this CTA's v columns, the two gates), so the walk itself touches shared memory only.
-// The state of a slot: per head D * Dv floats of S (row d, column j at d * Dv + j), D of z, then m.
+// The state of a slot: per head `head_stride` floats (a multiple of four, so that every head starts on 16 bytes):
+// D * Dv of S (row d, column j at d * Dv + j), D of z, then m.
 struct ScanArgs {
   const float* fused;     // [partials][N][total]: q (H D) | k (H D) | v (H Dv) | gate (H Dv) | i (H) | f (H)
   long long stride;
   int partials, total;
   const float* gate_bias; // [2 H]: input gates, then forget gates; or null
-  float* state;           // [slots][H][D Dv + D + 1]
+  float* state;           // [slots][H][head_stride], head_stride >= D Dv + D + 1
   const int* q_start;     // [S + 1]
   const int* state_slot;  // [S]; -1: the sequence is padding
   float* numerator;       // [N][H][Dv]
   float* denominator;     // [N][H]
   int heads, dim, vdim, cols, num_slots;
   float cap, q_scale, floor_;
+  int head_stride;
 };
 
 constexpr int SCAN_TOKENS = 8;
+constexpr int SCAN_THREADS = 256;   // all of them load and store; the first cols (+ 1) walk the tokens
+
+// A slice of a head's state matrix (rows d, columns col0 .. col0 + cols_here - 1 of [D][Dv]) between global memory
+// and shared memory (row stride ld), 16 bytes at a time where the columns allow.
+__device__ __forceinline__ void load_state_slice(float* S, int ld, const float* mine, int D, int Dv, int col0, int cols_here) {
+  if ((Dv & 3) == 0 && (col0 & 3) == 0 && (cols_here & 3) == 0 && (reinterpret_cast<uintptr_t>(mine) & 15) == 0) {
+    const int quads = cols_here >> 2;
+    for (int idx = threadIdx.x; idx < D * quads; idx += blockDim.x) {
+      const int d = idx / quads, j = (idx - d * quads) << 2;
+      const float4 v = *reinterpret_cast<const float4*>(mine + static_cast<size_t>(d) * Dv + col0 + j);
+      float* row = S + d * ld + j;
+      row[0] = v.x; row[1] = v.y; row[2] = v.z; row[3] = v.w;
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < D * cols_here; idx += blockDim.x) {
+      const int d = idx / cols_here, j = idx - d * cols_here;
+      S[d * ld + j] = mine[static_cast<size_t>(d) * Dv + col0 + j];
+    }
+  }
+}
+__device__ __forceinline__ void store_state_slice(const float* S, int ld, float* mine, int D, int Dv, int col0, int cols_here) {
+  if ((Dv & 3) == 0 && (col0 & 3) == 0 && (cols_here & 3) == 0 && (reinterpret_cast<uintptr_t>(mine) & 15) == 0) {
+    const int quads = cols_here >> 2;
+    for (int idx = threadIdx.x; idx < D * quads; idx += blockDim.x) {
+      const int d = idx / quads, j = (idx - d * quads) << 2;
+      const float* row = S + d * ld + j;
+      *reinterpret_cast<float4*>(mine + static_cast<size_t>(d) * Dv + col0 + j) = make_float4(row[0], row[1], row[2], row[3]);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < D * cols_here; idx += blockDim.x) {
+      const int d = idx / cols_here, c = idx - d * cols_here;
+      mine[static_cast<size_t>(d) * Dv + col0 + c] = S[d * ld + c];
+    }
+  }
+}
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
@@ -224,11 +352,8 @@ __global__ void matrix_memory_scan_kernel(const ScanArgs a) {
   float* ks = qs + SCAN_TOKENS * D;                 // [TOKENS][D]
   float* vs = ks + SCAN_TOKENS * D;                 // [TOKENS][cols]
   float* gates = vs + SCAN_TOKENS * a.cols;         // [TOKENS][2]: input gate, log forget gate
-  float* mine = a.state + (static_cast<size_t>(slot) * H + head) * (static_cast<size_t>(D) * Dv + D + 1);
-  for (int idx = threadIdx.x; idx < D * cols_here; idx += blockDim.x) {
-    const int d = idx / cols_here, j = idx - d * cols_here;
-    S[d * ld + j] = mine[static_cast<size_t>(d) * Dv + col0 + j];
-  }
+  float* mine = a.state + (static_cast<size_t>(slot) * H + head) * static_cast<size_t>(a.head_stride);
+  load_state_slice(S, ld, mine, D, Dv, col0, cols_here);
   if (keeps_z)
     for (int d = threadIdx.x; d < D; d += blockDim.x) S[d * ld + a.cols] = mine[static_cast<size_t>(D) * Dv + d];
   float m = mine[static_cast<size_t>(D) * Dv + D];
@@ -280,14 +405,408 @@ __global__ void matrix_memory_scan_kernel(const ScanArgs a) {
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < D * cols_here; idx += blockDim.x) {
-    const int d = idx / cols_here, c = idx - d * cols_here;
-    mine[static_cast<size_t>(d) * Dv + col0 + c] = S[d * ld + c];
-  }
+  store_state_slice(S, ld, mine, D, Dv, col0, cols_here);
   if (keeps_z) {
     for (int d = threadIdx.x; d < D; d += blockDim.x) mine[static_cast<size_t>(D) * Dv + d] = S[d * ld + a.cols];
     if (threadIdx.x == 0) mine[static_cast<size_t>(D) * Dv + D] = m;
   }
+}
+
+// ------------------------------------------------------------------------------------ matrix memory: chunks
+// The same recurrence for portions, as products over chunks of CHUNK tokens, every chunk on a CTA of its own.
+// With b_t the sum of the log forget gates from the chunk's start through token t, g_s = a_s - b_s,
+// N_t = max_{s <= t} g_s and M_t = max(m_0, N_t) (m_0: the running maximum the chunk starts from), the recurrence
+// unrolls to m_t = b_t + M_t and
+//   S_t^T q_t = exp(m_0 - M_t) S_0^T q_t + exp(N_t - M_t) sum_{s <= t} exp(g_s - N_t) (q_t . k_s) v_s
+//   S_L       = exp(m_0 - M_L) S_0 + exp(N_L - M_L) sum_s exp(g_s - N_L) k_s v_s^T      (z likewise, with v = 1)
+// where every exponent is <= 0.  Four launches:
+//   scores  every chunk by itself, once a head: the decayed scores exp(g_s - N_t) (q_t . k_s), N_t, b_t
+//   local   every chunk and slice of value columns: what the scores give (the second sum above and its normaliser,
+//           into the output buffers) and the chunk's own addition to the state (the last sum)
+//   carry   per sequence, head and column slice, chunk after chunk: the state each chunk starts from (written where
+//           the chunk's addition was) and its m_0; the state after the last chunk goes to the request's slot
+//   finish  every chunk by itself again: adds the part that comes from the state the chunk started from
+// All of it float32 on the CUDA cores: the state and what enters it stay 32-bit.  A chunk is the tokens
+// [64 c, 64 c + 64) of its sequence's portion; the grid holds ceil(N / 64) + sequences CTAs a head and slice, and a
+// CTA finds its sequence by walking the batch's lengths.
+constexpr int CHUNK = 64;
+constexpr int CHUNK_COLS = 32;
+constexpr int CHUNK_THREADS = 256;
+
+struct ChunkArgs {
+  ScanArgs scan;
+  float* chunk_state;     // [chunks][H][D Dv + D]: a chunk's addition to S and z, then the state it starts from
+  float* chunk_info;      // [chunks][H][4]: N_L, b_L, m_0
+  float* token_info;      // [N][H][4]: N_t, b_t, exp(g_t - N_L)
+  float* chunk_scores;    // [chunks][H][CHUNK][CHUNK]: the decayed scores
+  int num_seqs;
+};
+
+// (sequence, first token of the chunk within the batch, tokens in the chunk, index of the sequence's first chunk) of
+// chunk number `chunk` of the batch; false when the batch has fewer chunks.
+__device__ __forceinline__ bool find_chunk(const int* q_start, int num_seqs, int chunk, int* seq, int* first, int* here, int* base) {
+  int before = 0;
+  for (int s = 0; s < num_seqs; ++s) {
+    const int start = q_start[s], count = q_start[s + 1] - start;
+    const int chunks = (count + CHUNK - 1) / CHUNK;
+    if (chunk < before + chunks) {
+      const int c = chunk - before;
+      *seq = s;
+      *first = start + c * CHUNK;
+      *here = min(CHUNK, count - c * CHUNK);
+      *base = before;
+      return true;
+    }
+    before += chunks;
+  }
+  return false;
+}
+
+// rows [first, first + here) of a fused projection's columns [col, col + width) into shared memory (row stride ld),
+// each times `scale`, rows past `here` zeroed; 16 bytes at a time where the layout allows
+__device__ __forceinline__ void load_rows(float* dst, int ld, const ScanArgs& a, int first, int here, int col, int width, float scale) {
+  const bool wide = a.partials == 1 && (width & 3) == 0 && (col & 3) == 0 && (a.total & 3) == 0 &&
+                    (reinterpret_cast<uintptr_t>(a.fused) & 15) == 0;
+  if (wide) {
+    const int quads = width >> 2;
+    for (int idx = threadIdx.x; idx < CHUNK * quads; idx += blockDim.x) {
+      const int t = idx / quads, j = (idx - t * quads) << 2;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t < here) v = *reinterpret_cast<const float4*>(a.fused + static_cast<size_t>(first + t) * a.total + col + j);
+      float* row = dst + t * ld + j;
+      row[0] = v.x * scale; row[1] = v.y * scale; row[2] = v.z * scale; row[3] = v.w * scale;
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < CHUNK * width; idx += blockDim.x) {
+      const int t = idx / width, j = idx - t * width;
+      float v = 0.f;
+      if (t < here) v = sum_partials(a.fused + static_cast<size_t>(first + t) * a.total + col + j, a.stride, a.partials);
+      dst[t * ld + j] = v * scale;
+    }
+  }
+}
+
+// The decayed scores of a chunk, once a head: W[t][s] = exp(g_s - N_t) (q_t . k_s) for s <= t, 0 above the diagonal;
+// N_t, b_t and exp(g_t - N_L) of every token, N_L and b_L of the chunk.
+__global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_scores_kernel(const ChunkArgs c) {
+  extern __shared__ float chunk_shared[];
+  const ScanArgs& a = c.scan;
+  let_dependents_start();
+  wait_for_previous();
+  int seq, first, here, base;
+  if (!find_chunk(a.q_start, c.num_seqs, blockIdx.x, &seq, &first, &here, &base)) return;
+  const int slot = a.state_slot[seq];
+  if (slot < 0 || slot >= a.num_slots) return;
+  const int head = blockIdx.y, tid = threadIdx.x;
+  const int D = a.dim, Dv = a.vdim, H = a.heads;
+  const int ldq = D + 1;
+  float* Q = chunk_shared;                       // [CHUNK][ldq]
+  float* K = Q + CHUNK * ldq;                    // [CHUNK][ldq]
+  float* g_of = K + CHUNK * ldq;                 // [CHUNK] g_s (-inf past the chunk's end)
+  float* top_of = g_of + CHUNK;                  // [CHUNK] N_t
+  float* forget = top_of + CHUNK;                // [CHUNK] log forget gates
+  const int q_cols = H * D, gate_first = 2 * q_cols + 2 * H * Dv;
+  load_rows(Q, ldq, a, first, here, head * D, D, a.q_scale);
+  load_rows(K, ldq, a, first, here, q_cols + head * D, D, 1.f);
+  for (int idx = tid; idx < here * 2; idx += blockDim.x) {
+    const int t = idx >> 1, which = idx & 1;
+    const float* row = a.fused + static_cast<size_t>(first + t) * a.total;
+    float x = sum_partials(row + gate_first + which * H + head, a.stride, a.partials);
+    if (a.gate_bias != nullptr) x = __fadd_rn(x, a.gate_bias[which * H + head]);
+    x = a.cap * tanhf(x / a.cap);
+    if (which == 0) g_of[t] = x; else forget[t] = log_sigmoid(x);
+  }
+  __syncthreads();
+  const size_t chunk_index = static_cast<size_t>(blockIdx.x) * H + head;
+  if (tid == 0) {   // the chunk's running sums and maxima: a short walk by one thread
+    float b = 0.f, top = -INFINITY;
+    for (int t = 0; t < here; ++t) {
+      b += forget[t];
+      const float g = g_of[t] - b;
+      g_of[t] = g;
+      top = fmaxf(top, g);
+      top_of[t] = top;
+      forget[t] = b;
+    }
+    for (int t = here; t < CHUNK; ++t) { g_of[t] = -INFINITY; top_of[t] = top; }
+    c.chunk_info[chunk_index * 4] = top;
+    c.chunk_info[chunk_index * 4 + 1] = b;
+  }
+  __syncthreads();
+  if (tid < here) {
+    float* info = c.token_info + (static_cast<size_t>(first + tid) * H + head) * 4;
+    info[0] = top_of[tid];
+    info[1] = forget[tid];
+    info[2] = expf(g_of[tid] - top_of[CHUNK - 1]);
+  }
+  // thread (ty, tx) forms rows ty * 4 + i, columns tx + 16 j
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4] = {};
+  for (int d = 0; d < D; ++d) {
+    float q[4], k[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = Q[(ty * 4 + i) * ldq + d];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) k[j] = K[(tx + 16 * j) * ldq + d];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(q[i], k[j], acc[i][j]);
+  }
+  float* scores = c.chunk_scores + chunk_index * (CHUNK * CHUNK);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = ty * 4 + i, s = tx + 16 * j;
+      scores[t * CHUNK + s] = s <= t ? __fmul_rn(expf(g_of[s] - top_of[t]), acc[i][j]) : 0.f;
+    }
+}
+
+// What a chunk's own tokens give, for one slice of value columns: the decayed scores times v (and their row sums),
+// and the chunk's addition to the state, sum_s exp(g_s - N_L) k_s v_s^T.
+__global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_local_kernel(const ChunkArgs c) {
+  extern __shared__ float chunk_shared[];
+  const ScanArgs& a = c.scan;
+  let_dependents_start();
+  wait_for_previous();
+  int seq, first, here, base;
+  if (!find_chunk(a.q_start, c.num_seqs, blockIdx.x, &seq, &first, &here, &base)) return;
+  const int head = blockIdx.y, col0 = blockIdx.z * CHUNK_COLS;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int D = a.dim, Dv = a.vdim, H = a.heads;
+  const int cols_here = min(CHUNK_COLS, Dv - col0);
+  const bool first_slice = blockIdx.z == 0;
+  const int slot = a.state_slot[seq];
+  if (slot < 0 || slot >= a.num_slots) {   // a padding row: finite outputs, nothing else
+    for (int idx = tid; idx < here * cols_here; idx += blockDim.x) {
+      const int t = idx / cols_here, col = idx - t * cols_here;
+      a.numerator[(static_cast<size_t>(first + t) * H + head) * Dv + col0 + col] = 0.f;
+    }
+    if (first_slice)
+      for (int t = tid; t < here; t += blockDim.x) a.denominator[static_cast<size_t>(first + t) * H + head] = 1.f;
+    return;
+  }
+  const int ldq = D + 1, ldw = CHUNK + 1;
+  float* K = chunk_shared;                       // [CHUNK][ldq]
+  float* V = K + CHUNK * ldq;                    // [CHUNK][CHUNK_COLS]
+  float* W = V + CHUNK * CHUNK_COLS;             // [CHUNK][ldw]
+  float* take = W + CHUNK * ldw;                 // [CHUNK] exp(g_s - N_L), 0 past the chunk's end
+  const int q_cols = H * D, v_first = 2 * q_cols;
+  const size_t chunk_index = static_cast<size_t>(blockIdx.x) * H + head;
+  load_rows(K, ldq, a, first, here, q_cols + head * D, D, 1.f);
+  if (cols_here == CHUNK_COLS) load_rows(V, CHUNK_COLS, a, first, here, v_first + head * Dv + col0, CHUNK_COLS, 1.f);
+  else
+    for (int idx = tid; idx < CHUNK * CHUNK_COLS; idx += blockDim.x) {
+      const int t = idx / CHUNK_COLS, col = idx - t * CHUNK_COLS;
+      V[idx] = (t < here && col < cols_here)
+                   ? sum_partials(a.fused + static_cast<size_t>(first + t) * a.total + v_first + head * Dv + col0 + col, a.stride, a.partials)
+                   : 0.f;
+    }
+  const float* scores = c.chunk_scores + chunk_index * (CHUNK * CHUNK);
+  for (int idx = tid; idx < CHUNK * CHUNK / 4; idx += blockDim.x) {
+    const int t = idx / (CHUNK / 4), s = (idx - t * (CHUNK / 4)) * 4;
+    const float4 w = *reinterpret_cast<const float4*>(scores + t * CHUNK + s);
+    float* row = W + t * ldw + s;
+    row[0] = w.x; row[1] = w.y; row[2] = w.z; row[3] = w.w;
+  }
+  if (tid < CHUNK) take[tid] = tid < here ? c.token_info[(static_cast<size_t>(first + tid) * H + head) * 4 + 2] : 0.f;
+  __syncthreads();
+  {   // warp w rows w * 8 .. w * 8 + 7, lane its column
+    float acc[8] = {};
+    const int t_first = warp * 8;
+    for (int s = 0; s < min(here, t_first + 8); ++s) {
+      const float vv = V[s * CHUNK_COLS + lane];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = __fmaf_rn(W[(t_first + i) * ldw + s], vv, acc[i]);
+    }
+    if (lane < cols_here) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (t_first + i < here) a.numerator[(static_cast<size_t>(first + t_first + i) * H + head) * Dv + col0 + lane] = acc[i];
+    }
+    if (first_slice && tid < here) {
+      float rest = 0.f;
+      for (int s = 0; s <= tid; ++s) rest = __fadd_rn(rest, W[tid * ldw + s]);
+      a.denominator[static_cast<size_t>(first + tid) * H + head] = rest;
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < CHUNK * CHUNK_COLS; idx += blockDim.x) V[idx] = __fmul_rn(V[idx], take[idx / CHUNK_COLS]);
+  __syncthreads();
+  float* addition = c.chunk_state + chunk_index * (static_cast<size_t>(D) * Dv + D);
+  for (int d0 = warp * 8; d0 < D; d0 += 8 * (CHUNK_THREADS / 32)) {   // warp w rows d0 .. d0 + 7, lane its column
+    float acc[8] = {};
+    const int rows = min(8, D - d0);
+    for (int s = 0; s < here; ++s) {
+      const float vv = V[s * CHUNK_COLS + lane];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < rows) acc[r] = __fmaf_rn(K[s * ldq + d0 + r], vv, acc[r]);
+    }
+    if (lane < cols_here) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < rows) addition[static_cast<size_t>(d0 + r) * Dv + col0 + lane] = acc[r];
+    }
+  }
+  if (first_slice)
+    for (int d = tid; d < D; d += blockDim.x) {
+      float acc = 0.f;
+      for (int s = 0; s < here; ++s) acc = __fmaf_rn(take[s], K[s * ldq + d], acc);
+      addition[static_cast<size_t>(D) * Dv + d] = acc;
+    }
+}
+
+constexpr int CARRY_ROWS = 64;         // rows of a state slice one CTA of the carry kernel holds
+constexpr int CARRY_PER_THREAD = CARRY_ROWS * CHUNK_COLS / CHUNK_THREADS;
+
+// Elementwise and in order: a CTA holds CARRY_ROWS rows of one column slice of one head's state in registers and
+// walks the sequence's chunks; the next chunk's addition is on its way while this one's is used.
+__global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_carry_kernel(const ChunkArgs c, int row_groups) {
+  const ScanArgs& a = c.scan;
+  let_dependents_start();
+  wait_for_previous();
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int slice = blockIdx.x / row_groups, row0 = (blockIdx.x - slice * row_groups) * CARRY_ROWS, col0 = slice * CHUNK_COLS;
+  const int slot = a.state_slot[seq];
+  if (slot < 0 || slot >= a.num_slots) return;
+  const int D = a.dim, Dv = a.vdim, H = a.heads, tid = threadIdx.x;
+  const int cols_here = min(CHUNK_COLS, Dv - col0);
+  const bool holds_z = slice == 0, writes_info = blockIdx.x == 0;
+  int base = 0;   // the sequence's first chunk
+  for (int s = 0; s < seq; ++s) base += (a.q_start[s + 1] - a.q_start[s] + CHUNK - 1) / CHUNK;
+  const int chunks = (a.q_start[seq + 1] - a.q_start[seq] + CHUNK - 1) / CHUNK;
+  float* mine = a.state + (static_cast<size_t>(slot) * H + head) * static_cast<size_t>(a.head_stride);
+  const size_t per_chunk = static_cast<size_t>(D) * Dv + D;
+  // element i of a thread: row row0 + (tid + i * 256) / 32, column col0 + tid % 32
+  const int col = tid & (CHUNK_COLS - 1);
+  size_t offset[CARRY_PER_THREAD];
+  bool live[CARRY_PER_THREAD];
+  float held[CARRY_PER_THREAD], next[CARRY_PER_THREAD], held_z = 0.f, next_z = 0.f;
+#pragma unroll
+  for (int i = 0; i < CARRY_PER_THREAD; ++i) {
+    const int row = row0 + (tid + i * CHUNK_THREADS) / CHUNK_COLS;
+    live[i] = row < D && col < cols_here;
+    offset[i] = static_cast<size_t>(row) * Dv + col0 + col;
+    held[i] = live[i] ? mine[offset[i]] : 0.f;
+  }
+  const bool z_live = holds_z && tid < CARRY_ROWS && row0 + tid < D;
+  const size_t z_offset = static_cast<size_t>(D) * Dv + row0 + tid;
+  if (z_live) held_z = mine[z_offset];
+  float m0 = mine[static_cast<size_t>(D) * Dv + D];
+  float* addition = c.chunk_state + (static_cast<size_t>(base) * H + head) * per_chunk;
+  const float* info = c.chunk_info + (static_cast<size_t>(base) * H + head) * 4;
+  float top = 0.f, b = 0.f;
+  if (chunks > 0) {
+    top = info[0];
+    b = info[1];
+#pragma unroll
+    for (int i = 0; i < CARRY_PER_THREAD; ++i) next[i] = live[i] ? addition[offset[i]] : 0.f;
+    if (z_live) next_z = addition[z_offset];
+  }
+  for (int k = 0; k < chunks; ++k) {
+    float added[CARRY_PER_THREAD], added_z = next_z;
+#pragma unroll
+    for (int i = 0; i < CARRY_PER_THREAD; ++i) added[i] = next[i];
+    const float top_now = top, b_now = b;
+    float* here = addition;
+    if (k + 1 < chunks) {   // the next chunk's figures, asked for before this chunk's are used
+      addition += static_cast<size_t>(H) * per_chunk;
+      info += static_cast<size_t>(H) * 4;
+      top = info[0];
+      b = info[1];
+#pragma unroll
+      for (int i = 0; i < CARRY_PER_THREAD; ++i) next[i] = live[i] ? addition[offset[i]] : 0.f;
+      if (z_live) next_z = addition[z_offset];
+    }
+    const float top_all = fmaxf(m0, top_now);
+    const float keep = expf(m0 - top_all), take = expf(top_now - top_all);
+#pragma unroll
+    for (int i = 0; i < CARRY_PER_THREAD; ++i)
+      if (live[i]) {
+        here[offset[i]] = held[i];   // the state this chunk starts from
+        held[i] = __fmaf_rn(keep, held[i], __fmul_rn(take, added[i]));
+      }
+    if (z_live) {
+      here[z_offset] = held_z;
+      held_z = __fmaf_rn(keep, held_z, __fmul_rn(take, added_z));
+    }
+    if (writes_info && tid == 0) c.chunk_info[(static_cast<size_t>(base + k) * H + head) * 4 + 2] = m0;
+    m0 = b_now + top_all;
+  }
+#pragma unroll
+  for (int i = 0; i < CARRY_PER_THREAD; ++i)
+    if (live[i]) mine[offset[i]] = held[i];
+  if (z_live) mine[z_offset] = held_z;
+  if (writes_info && tid == 0) mine[static_cast<size_t>(D) * Dv + D] = m0;
+}
+
+__global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_finish_kernel(const ChunkArgs c) {
+  extern __shared__ float chunk_shared[];
+  const ScanArgs& a = c.scan;
+  let_dependents_start();
+  wait_for_previous();
+  int seq, first, here, base;
+  if (!find_chunk(a.q_start, c.num_seqs, blockIdx.x, &seq, &first, &here, &base)) return;
+  const int slot = a.state_slot[seq];
+  if (slot < 0 || slot >= a.num_slots) return;
+  const int head = blockIdx.y, col0 = blockIdx.z * CHUNK_COLS;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int D = a.dim, Dv = a.vdim, H = a.heads;
+  const int cols_here = min(CHUNK_COLS, Dv - col0);
+  const bool first_slice = blockIdx.z == 0;
+  const int ldq = D + 1, lds = CHUNK_COLS + 1;
+  float* Q = chunk_shared;                       // [CHUNK][ldq]
+  float* S = Q + CHUNK * ldq;                    // [D][lds]: the state the chunk starts from
+  float* z = S + static_cast<size_t>(D) * lds;   // [D]
+  const size_t chunk_index = static_cast<size_t>(blockIdx.x) * H + head;
+  const float* before = c.chunk_state + chunk_index * (static_cast<size_t>(D) * Dv + D);
+  const float m0 = c.chunk_info[chunk_index * 4 + 2];
+  load_rows(Q, ldq, a, first, here, head * D, D, a.q_scale);
+  for (int idx = tid; idx < D * CHUNK_COLS; idx += blockDim.x) {
+    const int d = idx / CHUNK_COLS, col = idx - d * CHUNK_COLS;
+    S[d * lds + col] = col < cols_here ? before[static_cast<size_t>(d) * Dv + col0 + col] : 0.f;
+  }
+  if (first_slice)
+    for (int d = tid; d < D; d += blockDim.x) z[d] = before[static_cast<size_t>(D) * Dv + d];
+  __syncthreads();
+  float acc[8] = {};
+  const int t_first = warp * 8;
+  for (int d = 0; d < D; ++d) {
+    const float sv = S[d * lds + lane];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = __fmaf_rn(Q[(t_first + i) * ldq + d], sv, acc[i]);
+  }
+  if (lane < cols_here) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = t_first + i;
+      if (t < here) {
+        const size_t token = static_cast<size_t>(first + t) * H + head;
+        const float top = c.token_info[token * 4], top_all = fmaxf(m0, top);
+        float* out = a.numerator + token * Dv + col0 + lane;
+        *out = __fmaf_rn(expf(m0 - top_all), acc[i], __fmul_rn(expf(top - top_all), *out));
+      }
+    }
+  }
+  if (first_slice && tid < here) {
+    const size_t token = static_cast<size_t>(first + tid) * H + head;
+    float dot = 0.f;
+    for (int d = 0; d < D; ++d) dot = __fmaf_rn(Q[tid * ldq + d], z[d], dot);
+    const float top = c.token_info[token * 4], b = c.token_info[token * 4 + 1], top_all = fmaxf(m0, top);
+    const float nq = __fmaf_rn(expf(m0 - top_all), dot, __fmul_rn(expf(top - top_all), a.denominator[token]));
+    a.denominator[token] = fmaxf(fabsf(nq), expf(-(b + top_all))) + a.floor_;
+  }
+}
+
+// Shared memory of the chunk kernels for heads of `dim`; 0 when they do not fit (the walk serves those).
+static size_t chunk_smem_bytes(int dim, size_t* scores_bytes, size_t* finish_bytes) {
+  *scores_bytes = (2ull * CHUNK * (dim + 1) + 3 * CHUNK) * sizeof(float);
+  const size_t local = (static_cast<size_t>(CHUNK) * (dim + 1) + CHUNK * CHUNK_COLS + static_cast<size_t>(CHUNK) * (CHUNK + 1) + CHUNK) * sizeof(float);
+  *finish_bytes = (static_cast<size_t>(CHUNK) * (dim + 1) + static_cast<size_t>(dim) * (CHUNK_COLS + 1) + dim) * sizeof(float);
+  const size_t limit = static_cast<size_t>(shrike_device().max_smem);
+  return (local <= limit && *finish_bytes <= limit && *scores_bytes <= limit) ? local : 0;
 }
 
 // -------------------------------------------------------------------------------------- matrix memory: out
@@ -328,31 +847,76 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) matrix_memory_out_kernel(cons
 }
 
 // ----------------------------------------------------------------------------------------------- route_top
-constexpr int ROUTE_WARPS = 4;
+// One block a token.  The logits: the block's warps share a row's columns (warp w the w-th run of 128 columns, and
+// so on), experts eight at a time with the eight weight rows' loads in flight together; the warps' sums meet in shared
+// memory in a fixed order.  Then, by the first warp: softmax, `top` rounds of a warp-wide argmax, the sum of the
+// chosen, and the shared expert's gate (its vector is one more row of the product).
+constexpr int ROUTE_WARPS = 8;
+constexpr int ROUTE_GROUP = 8;
 
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ shared_gate,
                  float* __restrict__ weights, int n, int width, int experts, int top, int columns, float renorm_eps) {
-  extern __shared__ float route_shared[];
+  extern __shared__ float route_shared[];   // [ROUTE_WARPS][rows] sums of the warps, then [rows] scores in the first row
   let_dependents_start();
   wait_for_previous();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int token = blockIdx.x * ROUTE_WARPS + warp;
-  if (token >= n) return;
-  float* score = route_shared + static_cast<size_t>(warp) * experts;
+  const int token = blockIdx.x;
   const T* row = x + static_cast<size_t>(token) * width;
   float* out = weights + static_cast<size_t>(token) * columns;
-  float best = -INFINITY;
-  for (int e = 0; e < experts; ++e) {
-    const float* w = router + static_cast<size_t>(e) * width;
-    float dot = 0.f;
-    for (int c = lane; c < width; c += 32) dot = __fmaf_rn(to_float(row[c]), w[c], dot);
-    dot = warp_sum(dot);
-    if (lane == 0) score[e] = dot;
-    best = fmaxf(best, dot);
+  // rows of the product: the experts, then (when there is one) the shared expert's gate vector
+  const int rows = experts + (columns > experts && shared_gate != nullptr ? 1 : 0);
+  const bool wide = (width & 3) == 0 && (reinterpret_cast<uintptr_t>(router) & 15) == 0 &&
+                    (shared_gate == nullptr || (reinterpret_cast<uintptr_t>(shared_gate) & 15) == 0) &&
+                    (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  float* partial = route_shared + static_cast<size_t>(warp) * rows;
+  for (int e0 = 0; e0 < rows; e0 += ROUTE_GROUP) {
+    float dot[ROUTE_GROUP] = {};
+    const float* from[ROUTE_GROUP];
+#pragma unroll
+    for (int g = 0; g < ROUTE_GROUP; ++g) {
+      const int e = min(e0 + g, rows - 1);   // rows past the end repeat the last one; their sums are dropped
+      from[g] = e < experts ? router + static_cast<size_t>(e) * width : shared_gate;
+    }
+    if (wide) {
+#pragma unroll 2
+      for (int c = (warp * 32 + lane) * 4; c < width; c += ROUTE_WARPS * 128) {
+        float xv[4], w[ROUTE_GROUP][4];
+        load4<T>(row + c, xv);
+#pragma unroll
+        for (int g = 0; g < ROUTE_GROUP; ++g) load4<float>(from[g] + c, w[g]);
+#pragma unroll
+        for (int g = 0; g < ROUTE_GROUP; ++g)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) dot[g] = __fmaf_rn(xv[k], w[g][k], dot[g]);
+      }
+    } else {
+      for (int c = warp * 32 + lane; c < width; c += ROUTE_WARPS * 32) {
+        const float xv = to_float(row[c]);
+#pragma unroll
+        for (int g = 0; g < ROUTE_GROUP; ++g) dot[g] = __fmaf_rn(xv, from[g][c], dot[g]);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < ROUTE_GROUP; ++g) {
+      const float sum = warp_sum(dot[g]);
+      if (lane == 0 && e0 + g < rows) partial[e0 + g] = sum;
+    }
   }
+  __syncthreads();
+  if (warp != 0) return;
+  float* score = route_shared;
+  float best = -INFINITY;
+  for (int e = lane; e < rows; e += 32) {
+    float sum = score[e];
+    for (int w = 1; w < ROUTE_WARPS; ++w) sum = __fadd_rn(sum, route_shared[static_cast<size_t>(w) * rows + e]);
+    score[e] = sum;
+    if (e < experts) best = fmaxf(best, sum);
+  }
+  best = warp_max(best);
   __syncwarp();
+  const float shared_dot = rows > experts ? score[experts] : 0.f;
   float total = 0.f;
   for (int e = lane; e < experts; e += 32) {
     const float p = expf(score[e] - best);
@@ -367,7 +931,7 @@ route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
   }
   __syncwarp();
   float chosen_sum = 0.f;
-  // `top` rounds of a warp-wide argmax; the lowest index wins a tie.  A pick is marked by negating its score.
+  // `top` rounds of a warp-wide argmax; the lowest index wins a tie.  A pick is marked by a negative score.
   for (int round = 0; round < top; ++round) {
     float mine = -1.f;
     int where = experts;
@@ -388,36 +952,41 @@ route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
   }
   const float inv = 1.0f / (chosen_sum + renorm_eps);
   for (int e = lane; e < experts; e += 32) out[e] = out[e] * inv;
-  if (columns > experts) {
-    float gate = 1.f;
-    if (shared_gate != nullptr) {
-      float dot = 0.f;
-      for (int c = lane; c < width; c += 32) dot = __fmaf_rn(to_float(row[c]), shared_gate[c], dot);
-      gate = 1.0f / (1.0f + expf(-warp_sum(dot)));
-    }
-    if (lane == 0) out[experts] = gate;
-  }
+  if (columns > experts && lane == 0) out[experts] = shared_gate != nullptr ? 1.0f / (1.0f + expf(-shared_dot)) : 1.f;
 }
 
 // ------------------------------------------------------------------------------------------ act_mul_blocks
 // gate_up [N][2 I]: all gate columns, then all up columns; I = experts * each + rest.  Column c belongs to
 // expert c / each, the last `rest` columns to the shared expert (weight column `experts`).
-template <typename T>
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 act_mul_blocks_kernel(const T* __restrict__ gate_up, const float* __restrict__ weights, T* __restrict__ out, int n, int inter,
                       int experts, int each, int columns, int act, float limit) {
   let_dependents_start();
   wait_for_previous();
+  // VEC consecutive columns a thread (one 16-byte access each way when VEC > 1; the launcher sees to it that a
+  // group never straddles two experts)
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+  const int groups = inter / VEC;
   for (int row = blockIdx.y; row < n; row += gridDim.y) {
     const T* in = gate_up + static_cast<size_t>(row) * 2 * inter;
     const float* w = weights + static_cast<size_t>(row) * columns;
     T* o = out + static_cast<size_t>(row) * inter;
-    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < inter; c += gridDim.x * blockDim.x) {
+    for (int group = blockIdx.x * blockDim.x + threadIdx.x; group < groups; group += gridDim.x * blockDim.x) {
+      const int c = group * VEC;
       const int block = c < experts * each ? c / each : experts;
       const float share = w[block];
-      // an expert the token did not choose contributes exactly nothing, whatever its gate and up columns hold
-      const float y = share == 0.f ? 0.f : __fmul_rn(act_times<T>(act, to_float(in[c]), to_float(in[inter + c]), limit), share);
-      o[c] = from_float<T>(y);
+      Pack r;
+      if (share == 0.f) {
+        // an expert the token did not choose contributes exactly nothing, whatever its gate and up columns hold
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(0.f);
+      } else {
+        const Pack g = *reinterpret_cast<const Pack*>(in + c), u = *reinterpret_cast<const Pack*>(in + inter + c);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(__fmul_rn(act_times<T>(act, to_float(g.v[j]), to_float(u.v[j]), limit), share));
+      }
+      *reinterpret_cast<Pack*>(o + c) = r;
     }
   }
 }
@@ -455,7 +1024,10 @@ SHRIKE_API int shrike_tanh_norm(float* resid, const float* const* data, const in
   }
   a.n = n;
   a.width = width;
-  const bool vec = width % 4 == 0;
+  bool vec = width % 4 == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0 && (reinterpret_cast<uintptr_t>(row_add) & 15) == 0;
+  for (int t = 0; t < num_terms; ++t) vec = vec && (reinterpret_cast<uintptr_t>(data[t]) & 15) == 0 && strides[t] % 4 == 0;
+  for (int k = 0; k < norms; ++k)
+    vec = vec && ((reinterpret_cast<uintptr_t>(weight[k]) | reinterpret_cast<uintptr_t>(bias[k]) | reinterpret_cast<uintptr_t>(out[k])) & 15) == 0;
   const int groups = vec ? width / 4 : width;
   const dim3 grid(max(1, min(32, (groups + 255) / 256)), max(1, min(n, 65535)));
   const bool bf16 = norms > 0 && out_dtype == SHRIKE_BF16;
@@ -479,9 +1051,11 @@ SHRIKE_API int shrike_head_prep(const float* fused, int partials, long long stri
   HeadPrepArgs a = {fused, stride, partials, total, bias, positions, inv_freq, rot, q_weight, k_weight, eps, q_out, keys,
                     values, slots, gate_out, n, heads, kv_heads, dim, vdim, padded, num_slots};
   const int units = heads + 2 * kv_heads + (gate_out != nullptr ? 1 : 0);
-  const long long work = static_cast<long long>(n) * units;
-  const unsigned blocks = static_cast<unsigned>((work + PREP_WARPS - 1) / PREP_WARPS);
-  const size_t smem = static_cast<size_t>(PREP_WARPS) * padded * sizeof(float);
+  // few tokens: a warp a unit, so that a step's heads are all under way at once; many: a block a token
+  const int per_token = n >= 1024 ? 1 : (units + PREP_WARPS - 1) / PREP_WARPS;
+  if (n > 2147483647 / 2 || per_token > 65535) return SHRIKE_BAD_ARGUMENT;
+  const dim3 blocks(static_cast<unsigned>(n), static_cast<unsigned>(per_token));
+  const size_t smem = (static_cast<size_t>(PREP_WARPS) * padded + (inv_freq != nullptr ? rot : 0)) * sizeof(float);
   if (dtype == SHRIKE_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(head_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     launch_dependent(head_prep_kernel<float>, blocks, PREP_WARPS * 32, smem, stream, a);
@@ -509,13 +1083,55 @@ static int scan_columns(int dim, int vdim, size_t* smem_out) {
   }
 }
 
+// `longest`: the most new tokens any sequence of the batch brings.  From CHUNK_FROM on the batch runs on the chunk
+// kernels (products over 64 tokens at a time, every chunk on its own CTA), below it on the walk (token by token:
+// decoding and short portions).  The chunk kernels need scratch: `chunk_state` (ceil(n / 64) + num_seqs) * heads *
+// (dim * vdim + dim) floats, `chunk_info` four floats a chunk and head, `token_info` two a token and head; with any of
+// them null the walk runs.  `chunk_scores`: 4096 floats a chunk and head; `token_info`: four a token and head.
+constexpr int CHUNK_FROM = 16;
+
+SHRIKE_API long long shrike_matrix_memory_chunks(int n, int num_seqs) { return (static_cast<long long>(n) + CHUNK - 1) / CHUNK + num_seqs; }
+
 SHRIKE_API int shrike_matrix_memory_scan(const float* fused, int partials, long long stride, int total, const float* gate_bias,
                                          float* state, const int* q_start, const int* state_slot, float* numerator,
                                          float* denominator, int num_seqs, int heads, int dim, int vdim, int num_slots,
-                                         float cap, float q_scale, float floor_, cudaStream_t stream) {
+                                         float cap, float q_scale, float floor_, int longest, int head_stride, int n,
+                                         float* chunk_state, float* chunk_info, float* token_info, float* chunk_scores,
+                                         cudaStream_t stream) {
   if (num_seqs <= 0) return SHRIKE_OK;
+  if (static_cast<long long>(head_stride) < static_cast<long long>(dim) * vdim + dim + 1) return SHRIKE_BAD_ARGUMENT;
   if (heads < 1 || dim < 1 || vdim < 1 || partials < 1 || !(cap > 0.f) || num_seqs > 65535 || heads > 65535) return SHRIKE_BAD_ARGUMENT;
   if (total < 2 * heads * dim + 2 * heads * vdim + 2 * heads) return SHRIKE_BAD_ARGUMENT;
+  size_t finish_bytes = 0, scores_bytes = 0;
+  const bool scratch = chunk_state != nullptr && chunk_info != nullptr && token_info != nullptr && chunk_scores != nullptr;
+  const size_t local_bytes = longest >= CHUNK_FROM && scratch ? chunk_smem_bytes(dim, &scores_bytes, &finish_bytes) : 0;
+  const int slices = (vdim + CHUNK_COLS - 1) / CHUNK_COLS;
+  if (local_bytes > 0 && slices <= 65535) {
+    static bool chunk_configured = false;
+    if (!chunk_configured) {
+      const int most = shrike_device().max_smem;
+      cudaError_t err = cudaFuncSetAttribute(matrix_memory_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+      if (err == cudaSuccess) err = cudaFuncSetAttribute(matrix_memory_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+      if (err == cudaSuccess) err = cudaFuncSetAttribute(matrix_memory_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+      if (err != cudaSuccess) return static_cast<int>(err);
+      chunk_configured = true;
+    }
+    ChunkArgs c = {};
+    c.scan = ScanArgs{fused, stride, partials, total, gate_bias, state, q_start, state_slot, numerator, denominator,
+                      heads, dim, vdim, CHUNK_COLS, num_slots, cap, q_scale, floor_, head_stride};
+    c.chunk_state = chunk_state;
+    c.chunk_info = chunk_info;
+    c.token_info = token_info;
+    c.chunk_scores = chunk_scores;
+    c.num_seqs = num_seqs;
+    const unsigned chunks = static_cast<unsigned>(shrike_matrix_memory_chunks(n, num_seqs));
+    launch_dependent(matrix_memory_scores_kernel, dim3(chunks, heads, 1), CHUNK_THREADS, scores_bytes, stream, c);
+    launch_dependent(matrix_memory_local_kernel, dim3(chunks, heads, slices), CHUNK_THREADS, local_bytes, stream, c);
+    const int row_groups = (dim + CARRY_ROWS - 1) / CARRY_ROWS;
+    launch_dependent(matrix_memory_carry_kernel, dim3(slices * row_groups, heads, num_seqs), CHUNK_THREADS, 0, stream, c, row_groups);
+    launch_dependent(matrix_memory_finish_kernel, dim3(chunks, heads, slices), CHUNK_THREADS, finish_bytes, stream, c);
+    return shrike_launch_status();
+  }
   size_t smem = 0;
   const int cols = scan_columns(dim, vdim, &smem);
   if (cols == 0) return SHRIKE_BAD_ARGUMENT;
@@ -527,10 +1143,9 @@ SHRIKE_API int shrike_matrix_memory_scan(const float* fused, int partials, long 
     configured = shrike_device().max_smem;
   }
   ScanArgs a = {fused, stride, partials, total, gate_bias, state, q_start, state_slot, numerator, denominator,
-                heads, dim, vdim, cols, num_slots, cap, q_scale, floor_};
+                heads, dim, vdim, cols, num_slots, cap, q_scale, floor_, head_stride};
   const dim3 grid((vdim + cols - 1) / cols, heads, num_seqs);
-  const int threads = (cols + 1 + 31) / 32 * 32;
-  launch_dependent(matrix_memory_scan_kernel, grid, threads, smem, stream, a);
+  launch_dependent(matrix_memory_scan_kernel, grid, SCAN_THREADS, smem, stream, a);
   return shrike_launch_status();
 }
 
@@ -553,9 +1168,9 @@ SHRIKE_API int shrike_matrix_memory_out(const float* numerator, const float* den
 SHRIKE_API int shrike_route_top(const void* x, int dtype, const float* router, const float* shared_gate, float* weights, int n,
                                 int width, int experts, int top, int columns, float renorm_eps, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
-  if (experts < 1 || top < 1 || top > experts || experts > 2048 || (columns != experts && columns != experts + 1)) return SHRIKE_BAD_ARGUMENT;
-  const unsigned blocks = static_cast<unsigned>((n + ROUTE_WARPS - 1) / ROUTE_WARPS);
-  const size_t smem = static_cast<size_t>(ROUTE_WARPS) * experts * sizeof(float);
+  if (experts < 1 || top < 1 || top > experts || experts > 1024 || (columns != experts && columns != experts + 1)) return SHRIKE_BAD_ARGUMENT;
+  const unsigned blocks = static_cast<unsigned>(n);
+  const size_t smem = static_cast<size_t>(ROUTE_WARPS) * (experts + 1) * sizeof(float);
   if (dtype == SHRIKE_F32)
     launch_dependent(route_top_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, static_cast<const float*>(x), router,
                      shared_gate, weights, n, width, experts, top, columns, renorm_eps);
@@ -571,13 +1186,28 @@ SHRIKE_API int shrike_act_mul_blocks(const void* gate_up, const float* weights, 
   if (n <= 0) return SHRIKE_OK;
   if (inter < 1 || experts < 1 || each < 1 || experts * each > inter || !known_activation(act)) return SHRIKE_BAD_ARGUMENT;
   if (experts * each < inter && columns != experts + 1) return SHRIKE_BAD_ARGUMENT;
-  const dim3 grid(max(1, min(64, (inter + 255) / 256)), max(1, min(n, 65535)));
-  if (dtype == SHRIKE_F32)
-    launch_dependent(act_mul_blocks_kernel<float>, grid, 256, 0, stream, static_cast<const float*>(gate_up), weights,
-                     static_cast<float*>(out), n, inter, experts, each, columns, act, limit);
-  else if (dtype == SHRIKE_BF16)
-    launch_dependent(act_mul_blocks_kernel<__nv_bfloat16>, grid, 256, 0, stream, static_cast<const __nv_bfloat16*>(gate_up), weights,
-                     static_cast<__nv_bfloat16*>(out), n, inter, experts, each, columns, act, limit);
-  else return SHRIKE_BAD_ARGUMENT;
+  const int wide_f32 = 4, wide_bf16 = 8;
+  const bool aligned = (reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+  if (dtype == SHRIKE_F32) {
+    const bool vec = aligned && inter % wide_f32 == 0 && each % wide_f32 == 0;
+    const int groups = vec ? inter / wide_f32 : inter;
+    const dim3 grid(max(1, min(64, (groups + 255) / 256)), max(1, min(n, 65535)));
+    if (vec)
+      launch_dependent(act_mul_blocks_kernel<float, 4>, grid, 256, 0, stream, static_cast<const float*>(gate_up), weights,
+                       static_cast<float*>(out), n, inter, experts, each, columns, act, limit);
+    else
+      launch_dependent(act_mul_blocks_kernel<float, 1>, grid, 256, 0, stream, static_cast<const float*>(gate_up), weights,
+                       static_cast<float*>(out), n, inter, experts, each, columns, act, limit);
+  } else if (dtype == SHRIKE_BF16) {
+    const bool vec = aligned && inter % wide_bf16 == 0 && each % wide_bf16 == 0;
+    const int groups = vec ? inter / wide_bf16 : inter;
+    const dim3 grid(max(1, min(64, (groups + 255) / 256)), max(1, min(n, 65535)));
+    if (vec)
+      launch_dependent(act_mul_blocks_kernel<__nv_bfloat16, 8>, grid, 256, 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
+                       weights, static_cast<__nv_bfloat16*>(out), n, inter, experts, each, columns, act, limit);
+    else
+      launch_dependent(act_mul_blocks_kernel<__nv_bfloat16, 1>, grid, 256, 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
+                       weights, static_cast<__nv_bfloat16*>(out), n, inter, experts, each, columns, act, limit);
+  } else return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
 }

@@ -54,6 +54,11 @@ _LIMITS = {
     "head_scale": "the head size must be a multiple of 4 and the array 16-byte aligned",
     "act_mul": "the activation must be one the kernels know and the run length divide the row",
     "gemm_tcgen05": "K must be a multiple of 8 and the operands 16-byte aligned",
+    "tanh_norm": "at most four pending sums and two norms",
+    "head_prep": "heads of at most 8192 elements, rotated dimensions even and at most the head's, the row at least as wide as q, k, v and gates",
+    "matrix_memory_scan": "a positive gate cap, at most 65535 sequences and heads, the row at least as wide as q, k, v, gate and both gate columns, the state's heads at least dim * vdim + dim + 1 floats",
+    "route_top": "at most 1024 experts, 1 <= top <= experts, the weights [N, experts] or [N, experts + 1]",
+    "act_mul_blocks": "experts * each columns at most, the rest the shared expert's, which needs the weights' last column",
     "paged_attention_bf16": "at most 65535 sequences and heads, heads a multiple of kv heads, at most 32 splits",
 }
 
@@ -112,6 +117,7 @@ class CudaOps:
         self._arrivals = None    # per kv head: splits of single-token attention that have finished
         self._portion_scratch = None   # partial rows of the portions kernel when a query tile's keys are split
         self._portion_tiles = None
+        self._memory_scratch = None   # what the matrix memory's chunk kernels hand from one launch to the next
         self.portion_splits = 0  # 0: the kernel library's rule; n: that many key splits for portions (tests)
         self.generation = 0      # grows when the scratch moves
         self._held_stream = None
@@ -144,10 +150,12 @@ class CudaOps:
         lib.shrike_act_mul_limit.argtypes = [_P, _P, _I, _I, _I, _I, _I, _F, _P]
         lib.shrike_tanh_norm.argtypes = [_P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P]
         lib.shrike_head_prep.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P] + [_I] * 8 + [_P]
-        lib.shrike_matrix_memory_scan.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P, _P] + [_I] * 5 + [_F, _F, _F, _P]
+        lib.shrike_matrix_memory_scan.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P, _P] + [_I] * 5 + [_F, _F, _F, _I, _I, _I, _P, _P, _P, _P, _P]
         lib.shrike_matrix_memory_out.argtypes = [_P, _P, _P, _I, _LL, _I, _I, _P, _F, _P, _I, _I, _I, _I, _P]
         lib.shrike_route_top.argtypes = [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P]
         lib.shrike_act_mul_blocks.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P]
+        lib.shrike_matrix_memory_chunks.argtypes = [_I, _I]
+        lib.shrike_matrix_memory_chunks.restype = _LL
         for name in ("shrike_embed_scaled", "shrike_act_mul_limit", "shrike_tanh_norm", "shrike_head_prep",
                      "shrike_matrix_memory_scan", "shrike_matrix_memory_out", "shrike_route_top", "shrike_act_mul_blocks"):
             getattr(lib, name).restype = _I
@@ -721,12 +729,15 @@ class CudaOps:
             self.code, fused.shape[-2], num_heads, num_kv_heads, dim, vdim, padded, num_slots, self._stream()), "head_prep")
 
     def matrix_memory(self, fused, gate_bias, state, q_start, state_slot, numerator, denominator, weight, eps, out,
-                      num_seqs, num_heads, dim, vdim, cap, floor):
-        """The matrix-memory recurrence over the batch's new tokens and its gated, normed output.
+                      num_seqs, num_heads, dim, vdim, cap, floor, longest=0):
+        """The matrix-memory recurrence over the batch's new tokens and its gated, normed output.  `longest`: the
+        most new tokens a sequence of the batch brings (the batch's shape, known on the host); long portions run
+        as products over 64 tokens at a time, short ones and single tokens as a walk, with the same result.
 
         `fused` ([N, total] float32 or a K-split stack): q (H dim) | k (H dim) | v (H vdim) | output gate
         (H vdim) | input gate (H) | forget gate (H); `gate_bias` float32 [2 H].  `state` float32
-        [slots, H, dim * vdim + dim + 1] (S, z, m of every head) is read and left updated for the slots
+        [slots, H, at least dim * vdim + dim + 1] (S, z, m of every head; a multiple of four floats keeps the heads
+        on 16-byte borders) is read and left updated for the slots
         `state_slot` names (-1: the sequence is skipped).  `out` [N, H * vdim]: each head's o over its root
         mean square, times `weight`, times the sigmoid of the output gate."""
         _dense(fused, torch.float32, "fused projection")
@@ -734,13 +745,25 @@ class CudaOps:
         _dense(out, self.dtype, "mixer output")
         partials, stride = self._stack(fused)
         total, n = fused.shape[-1], fused.shape[-2]
-        if tuple(state.shape[1:]) != (num_heads, dim * vdim + dim + 1):
+        if state.dim() != 3 or state.shape[1] != num_heads or state.shape[2] < dim * vdim + dim + 1:
             raise KernelError(f"state {tuple(state.shape)} does not fit {num_heads} heads of {dim} x {vdim}")
-        self.launches += 2
+        chunk_state = chunk_info = token_info = chunk_scores = None
+        if longest >= 16:   # long portions: products over chunks of 64 tokens, which hand each other scratch
+            chunks = self.core.shrike_matrix_memory_chunks(n, num_seqs)
+            sizes = (chunks * num_heads * (dim * vdim + dim), chunks * num_heads * 4, n * num_heads * 4, chunks * num_heads * 4096)
+            held = self._memory_scratch
+            if held is None or any(t.numel() < size for t, size in zip(held, sizes)):
+                held = tuple(torch.empty(max(2 * size, 1024), dtype=torch.float32, device=self.device) for size in sizes)
+                self._memory_scratch = held
+                self.generation += 1
+            chunk_state, chunk_info, token_info, chunk_scores = held
+        self.launches += 5 if chunk_state is not None else 2
         _check(self.core.shrike_matrix_memory_scan(
             _ptr(fused), partials, stride, total, _ptr(gate_bias), _ptr(state), _ptr(q_start), _ptr(state_slot),
             _ptr(numerator), _ptr(denominator), num_seqs, num_heads, dim, vdim, state.shape[0], cap, float(dim) ** -0.5, floor,
-            self._stream()), "matrix_memory_scan")
+            int(longest), state.shape[2], n, _ptr(chunk_state), _ptr(chunk_info), _ptr(token_info), _ptr(chunk_scores),
+            self._stream()),
+            "matrix_memory_scan")
         _check(self.core.shrike_matrix_memory_out(
             _ptr(numerator), _ptr(denominator), _ptr(fused), partials, stride, total, 2 * num_heads * dim + num_heads * vdim,
             _ptr(weight), eps, _ptr(out), self.code, n, num_heads, vdim, self._stream()), "matrix_memory_out")

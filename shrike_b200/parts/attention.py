@@ -230,6 +230,9 @@ class GatedHeadAttention:
         rows = [tensors.pop("q_proj.weight"), tensors.pop("k_proj.weight"), tensors.pop("v_proj.weight")]
         if spec.head_gate:
             rows.append(tensors.pop("gate.weight").to(rows[0].dtype))
+        extra = -sum(r.shape[0] for r in rows) % 16   # rows of zeros: output rows of a whole number of 64 bytes
+        if extra:
+            rows.append(rows[0].new_zeros(extra, spec.width))
         self.w_fused = torch.cat(rows).contiguous()
         self.total = self.w_fused.shape[0]
         self.bias = None

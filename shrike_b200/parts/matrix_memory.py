@@ -9,7 +9,7 @@ f_t = logsigmoid(cap tanh((w_f x + b_f) / cap)), and a running maximum m (m_0 = 
 
 Each head's o_t is divided by its root mean square; the heads, side by side, are scaled by one
 weight, gated by sigmoid(Wg x) and projected.  S, z and m of every head are the request's state: one
-float32 slot `[heads, dim * vdim + dim + 1]`, zeroed by the step function when the request is opened
+float32 slot `[heads, dim * vdim + dim + 1 (rounded up to four)]`, zeroed by the step function when the request is opened
 (so m_0 = 0 needs nothing of its own), read and left updated by the scan kernel, whatever the cut of
 the prompt.  All six projections are one matrix product; gates, decays and the state are 32-bit.
 """
@@ -19,6 +19,15 @@ from __future__ import annotations
 import torch
 
 from .base import ParamSpec, StateNeed, register_part
+
+
+def padded_rows(matrix: torch.Tensor, multiple: int = 16) -> torch.Tensor:
+    """`matrix` with rows of zeros added up to a multiple: a fused projection whose output rows are a whole
+    number of 64 bytes gets the library's aligned product kernels."""
+    extra = -matrix.shape[0] % multiple
+    if extra:
+        matrix = torch.cat([matrix, matrix.new_zeros(extra, matrix.shape[1])])
+    return matrix.contiguous()
 
 
 class MatrixMemory:
@@ -42,7 +51,8 @@ class MatrixMemory:
 
     @staticmethod
     def state_shape(spec) -> tuple:
-        return (spec.num_heads, spec.head_dim * spec.value_dim + spec.head_dim + 1)
+        floats = spec.head_dim * spec.value_dim + spec.head_dim + 1      # S, z and m of a head
+        return (spec.num_heads, -(-floats // 4) * 4)                      # every head starts on a 16-byte border
 
     @staticmethod
     def cache_needs(spec) -> list:
@@ -53,7 +63,7 @@ class MatrixMemory:
         first = tensors["q_proj.weight"]
         rows = [tensors.pop(name) for name in ("q_proj.weight", "k_proj.weight", "v_proj.weight", "gate.weight")]
         rows += [tensors.pop("input_gate.weight").to(first.dtype), tensors.pop("forget_gate.weight").to(first.dtype)]
-        self.w_fused = torch.cat(rows).contiguous()
+        self.w_fused = padded_rows(torch.cat(rows))
         self.total = self.w_fused.shape[0]
         self.gate_bias = torch.cat([tensors.pop("input_gate.bias"), tensors.pop("forget_gate.bias")]).to(torch.float32).contiguous()
         self.norm_weight = tensors.pop("norm.weight").to(torch.float32).contiguous()
@@ -72,7 +82,7 @@ class MatrixMemory:
         out = rt.buffer("memory_out", (n, self.out_width), rt.act_dtype)
         ops.matrix_memory(fused, self.gate_bias, ctx.storage.state[run.cache], ctx.q_start, ctx.state_slot, numerator,
                           denominator, self.norm_weight, spec.eps, out, ctx.num_seqs, spec.num_heads, spec.head_dim,
-                          spec.value_dim, spec.gate_cap, spec.denominator_floor)
+                          spec.value_dim, spec.gate_cap, spec.denominator_floor, longest=ctx.max_q_len)
         delta = rt.buffer("memory_delta", (n, spec.width), torch.float32)
         return ops.linear(out, self.w_o, delta, allow_partials=True)
 

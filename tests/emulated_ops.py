@@ -85,7 +85,7 @@ class EmulatedOps:
             self.kv_write(pad(k, num_kv_heads, dim)[stored], pad(v, num_kv_heads, vdim)[stored], keys, values, slots[stored])
 
     def matrix_memory(self, fused, gate_bias, state, q_start, state_slot, numerator, denominator, weight, eps, out,
-                      num_seqs, num_heads, dim, vdim, cap, floor):
+                      num_seqs, num_heads, dim, vdim, cap, floor, longest=0):
         if fused.dim() == 3:
             fused = fused.sum(0)
         x = fused.float()

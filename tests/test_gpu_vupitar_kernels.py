@@ -259,7 +259,7 @@ def memory_case(heads, dim, vdim, cap, n, seed):
     return weights, h, spec, fused
 
 
-def run_memory(ops, dtype, fused, weights, spec, cuts, state, slot, partials=1):
+def run_memory(ops, dtype, fused, weights, spec, cuts, state, slot, partials=1, walk=False):
     heads, dim, vdim = spec["heads"], spec["dim"], spec["vdim"]
     outs, position = [], 0
     bias = torch.cat([weights["m.i.b"], weights["m.f.b"]]).float().to(DEV)
@@ -272,7 +272,8 @@ def run_memory(ops, dtype, fused, weights, spec, cuts, state, slot, partials=1):
         den = torch.empty(cut, heads, dtype=torch.float32, device=DEV)
         q_start = torch.tensor([0, cut], dtype=torch.int32, device=DEV)
         ops.matrix_memory(piece, bias, state, q_start, torch.tensor([slot], dtype=torch.int32, device=DEV), num, den,
-                          weights["m.norm"].float().to(DEV), 1e-5, out, 1, heads, dim, vdim, spec["gate_cap"], 1e-6)
+                          weights["m.norm"].float().to(DEV), 1e-5, out, 1, heads, dim, vdim, spec["gate_cap"], 1e-6,
+                          longest=0 if walk else cut)
         outs.append(out)
         position += cut
     return torch.cat(outs)
@@ -280,7 +281,7 @@ def run_memory(ops, dtype, fused, weights, spec, cuts, state, slot, partials=1):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,dim,vdim,cap", [(2, 48, 48, 12.0), (3, 16, 24, 8.0), (1, 64, 64, 15.0), (2, 40, 8, 1.5), (3, 8, 40, 2.5),
-                                                (1, 128, 256, 15.0), (2, 300, 70, 6.0)])
+                                                (1, 128, 256, 15.0), (2, 256, 40, 6.0), (2, 300, 70, 6.0)])
 def test_matrix_memory_whole_in_portions_and_token_by_token(dtype, heads, dim, vdim, cap):
     ops = cuda_ops(dtype)
     n = 150
@@ -289,15 +290,19 @@ def test_matrix_memory_whole_in_portions_and_token_by_token(dtype, heads, dim, v
     want = pv.matrix_memory(h.double(), weights, "m", spec, 1e-5, False, trace=trace)
     m, S, z = trace[0]
     tol = 2e-4 if dtype == torch.float32 else 4e-2
-    state = torch.zeros(3, heads, dim * vdim + dim + 1, dtype=torch.float32, device=DEV)
+    state = torch.zeros(3, heads, -(-(dim * vdim + dim + 1) // 4) * 4, dtype=torch.float32, device=DEV)
     state[1] = float("nan")                           # a neighbour's slot: never read, never written
-    for slot, cuts, partials in ((0, [n], 1), (2, [1, 2, 7, 64, 3, 1, 1, 71], 3)):
-        got = run_memory(ops, dtype, fused, weights, spec, cuts, state, slot, partials)
+    # whole (products over chunks of 64), the same as a walk token by token inside one launch, and cut into portions
+    # that meet both forms and leave a chunk part full
+    for slot, cuts, partials, walk in ((0, [n], 1, False), (0, [n], 1, True), (2, [1, 2, 7, 64, 3, 1, 1, 71], 3, False)):
+        state[slot].zero_()
+        got = run_memory(ops, dtype, fused, weights, spec, cuts, state, slot, partials, walk)
         close(got, want, tol, f"cuts {cuts}")
         held = state[slot].cpu().double()
-        close(held[:, : dim * vdim].view(heads, dim, vdim), S, 2e-4, "S")
-        close(held[:, dim * vdim: dim * vdim + dim], z, 2e-4, "z")
-        close(held[:, -1], m, 1e-4, "m")
+        size = float(S.abs().max())              # the state's entries grow with the sequence: judged against their size
+        close(held[:, : dim * vdim].view(heads, dim, vdim) / size, S / size, 1e-5, "S")
+        close(held[:, dim * vdim: dim * vdim + dim] / float(z.abs().max()), z / float(z.abs().max()), 1e-5, "z")
+        close(held[:, dim * vdim + dim], m, 1e-4, "m")
     assert torch.isnan(state[1]).all()
     state[0].zero_()                                  # the slot's next owner, token by token
     got = run_memory(ops, dtype, fused[:40], weights, spec, [1] * 40, state, 0)
@@ -307,7 +312,7 @@ def test_matrix_memory_whole_in_portions_and_token_by_token(dtype, heads, dim, v
 def test_matrix_memory_skips_padding_rows_and_leaves_them_finite():
     ops = cuda_ops(torch.float32)
     weights, h, spec, fused = memory_case(2, 16, 16, 5.0, 6, seed=3)
-    state = torch.zeros(2, 2, 16 * 16 + 16 + 1, dtype=torch.float32, device=DEV)
+    state = torch.zeros(2, 2, 16 * 16 + 16 + 1, dtype=torch.float32, device=DEV)   # heads that start off a 16-byte border
     out = torch.full((6, 32), float("nan"), dtype=torch.float32, device=DEV)
     num, den = torch.full((6, 32), float("nan"), device=DEV), torch.full((6, 2), float("nan"), device=DEV)
     bias = torch.cat([weights["m.i.b"], weights["m.f.b"]]).float().to(DEV)

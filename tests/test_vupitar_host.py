@@ -133,7 +133,7 @@ def test_a_request_holds_one_state_slot_and_the_pages_of_its_chunk(tmp_path):
     assert sorted((g.chunk, g.head_dim, g.num_kv_heads, g.cache_ids) for g in groups) == [(20, 32, 2, (0, 1, 3)), (33, 16, 3, (2, 4))]
     state = session.runner.storage.state
     assert sorted(state) == [0, 1, 2, 3, 4]
-    assert tuple(state[0].shape) == (2, 3, 16 * 24 + 16 + 1) and tuple(state[2].shape) == (2, 2, 24 * 8 + 24 + 1)
+    assert tuple(state[0].shape) == (2, 3, 16 * 24 + 16 + 4) and tuple(state[2].shape) == (2, 2, 24 * 8 + 24 + 4)
     tokens = random_tokens(211, 70, 5)
     session.step({"step": 0, "entries": [{"id": "a", "tokens": tokens, "want": []}], "end": []})
     tables = session.live["a"][0].tables
