@@ -465,6 +465,8 @@ __device__ __forceinline__ bool find_chunk(const int* q_start, int num_seqs, int
 // rows [first, first + here) of a fused projection's columns [col, col + width) into shared memory (row stride ld),
 // each times `scale`, rows past `here` zeroed; 16 bytes at a time where the layout allows
 __device__ __forceinline__ void load_rows(float* dst, int ld, const ScanArgs& a, int first, int here, int col, int width, float scale) {
+  if (ld > width && ld - width < 4)   // rows padded to a multiple of four: the padding reads as zeros
+    for (int idx = threadIdx.x; idx < CHUNK * (ld - width); idx += blockDim.x) dst[(idx / (ld - width)) * ld + width + idx % (ld - width)] = 0.f;
   const bool wide = a.partials == 1 && (width & 3) == 0 && (col & 3) == 0 && (a.total & 3) == 0 &&
                     (reinterpret_cast<uintptr_t>(a.fused) & 15) == 0;
   if (wide) {
@@ -587,7 +589,9 @@ __global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_local_kernel(cons
       for (int t = tid; t < here; t += blockDim.x) a.denominator[static_cast<size_t>(first + t) * H + head] = 1.f;
     return;
   }
-  const int ldq = D + 1, ldw = CHUNK + 1;
+  // K and the scores are read here a row at a time by all lanes alike (broadcasts), so their rows keep 16-byte
+  // alignment and are read four elements a load
+  const int ldq = (D + 3) & ~3, ldw = CHUNK;
   float* K = chunk_shared;                       // [CHUNK][ldq]
   float* V = K + CHUNK * ldq;                    // [CHUNK][CHUNK_COLS]
   float* W = V + CHUNK * CHUNK_COLS;             // [CHUNK][ldw]
@@ -607,18 +611,25 @@ __global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_local_kernel(cons
   for (int idx = tid; idx < CHUNK * CHUNK / 4; idx += blockDim.x) {
     const int t = idx / (CHUNK / 4), s = (idx - t * (CHUNK / 4)) * 4;
     const float4 w = *reinterpret_cast<const float4*>(scores + t * CHUNK + s);
-    float* row = W + t * ldw + s;
-    row[0] = w.x; row[1] = w.y; row[2] = w.z; row[3] = w.w;
+    *reinterpret_cast<float4*>(W + t * ldw + s) = w;
   }
   if (tid < CHUNK) take[tid] = tid < here ? c.token_info[(static_cast<size_t>(first + tid) * H + head) * 4 + 2] : 0.f;
   __syncthreads();
   {   // warp w rows w * 8 .. w * 8 + 7, lane its column
     float acc[8] = {};
     const int t_first = warp * 8;
-    for (int s = 0; s < min(here, t_first + 8); ++s) {
-      const float vv = V[s * CHUNK_COLS + lane];
+    for (int s = 0; s < min(here, t_first + 8); s += 4) {   // the scores past a row's own token and past the chunk are 0
+      float vv[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = __fmaf_rn(W[(t_first + i) * ldw + s], vv, acc[i]);
+      for (int k = 0; k < 4; ++k) vv[k] = V[(s + k) * CHUNK_COLS + lane];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 w = *reinterpret_cast<const float4*>(W + (t_first + i) * ldw + s);
+        acc[i] = __fmaf_rn(w.x, vv[0], acc[i]);
+        acc[i] = __fmaf_rn(w.y, vv[1], acc[i]);
+        acc[i] = __fmaf_rn(w.z, vv[2], acc[i]);
+        acc[i] = __fmaf_rn(w.w, vv[3], acc[i]);
+      }
     }
     if (lane < cols_here) {
 #pragma unroll
@@ -640,9 +651,13 @@ __global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_local_kernel(cons
     const int rows = min(8, D - d0);
     for (int s = 0; s < here; ++s) {
       const float vv = V[s * CHUNK_COLS + lane];
-#pragma unroll
-      for (int r = 0; r < 8; ++r)
-        if (r < rows) acc[r] = __fmaf_rn(K[s * ldq + d0 + r], vv, acc[r]);
+      // K's rows are padded to a multiple of four (zeros), so both loads stay inside the row
+      const float4 lo = *reinterpret_cast<const float4*>(K + s * ldq + d0);
+      const float4 hi = rows > 4 ? *reinterpret_cast<const float4*>(K + s * ldq + d0 + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      acc[0] = __fmaf_rn(lo.x, vv, acc[0]); acc[1] = __fmaf_rn(lo.y, vv, acc[1]);
+      acc[2] = __fmaf_rn(lo.z, vv, acc[2]); acc[3] = __fmaf_rn(lo.w, vv, acc[3]);
+      acc[4] = __fmaf_rn(hi.x, vv, acc[4]); acc[5] = __fmaf_rn(hi.y, vv, acc[5]);
+      acc[6] = __fmaf_rn(hi.z, vv, acc[6]); acc[7] = __fmaf_rn(hi.w, vv, acc[7]);
     }
     if (lane < cols_here) {
 #pragma unroll
@@ -756,7 +771,7 @@ __global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_finish_kernel(con
   const int D = a.dim, Dv = a.vdim, H = a.heads;
   const int cols_here = min(CHUNK_COLS, Dv - col0);
   const bool first_slice = blockIdx.z == 0;
-  const int ldq = D + 1, lds = CHUNK_COLS + 1;
+  const int ldq = (D + 3) & ~3, lds = CHUNK_COLS + 1;   // Q's rows are read by all lanes alike: 16-byte aligned, four a load
   float* Q = chunk_shared;                       // [CHUNK][ldq]
   float* S = Q + CHUNK * ldq;                    // [D][lds]: the state the chunk starts from
   float* z = S + static_cast<size_t>(D) * lds;   // [D]
@@ -764,19 +779,28 @@ __global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_finish_kernel(con
   const float* before = c.chunk_state + chunk_index * (static_cast<size_t>(D) * Dv + D);
   const float m0 = c.chunk_info[chunk_index * 4 + 2];
   load_rows(Q, ldq, a, first, here, head * D, D, a.q_scale);
-  for (int idx = tid; idx < D * CHUNK_COLS; idx += blockDim.x) {
-    const int d = idx / CHUNK_COLS, col = idx - d * CHUNK_COLS;
-    S[d * lds + col] = col < cols_here ? before[static_cast<size_t>(d) * Dv + col0 + col] : 0.f;
+  if (cols_here < CHUNK_COLS) {
+    for (int idx = tid; idx < D * lds; idx += blockDim.x) S[idx] = 0.f;
+    __syncthreads();
   }
+  load_state_slice(S, lds, before, D, Dv, col0, cols_here);
   if (first_slice)
     for (int d = tid; d < D; d += blockDim.x) z[d] = before[static_cast<size_t>(D) * Dv + d];
   __syncthreads();
   float acc[8] = {};
   const int t_first = warp * 8;
-  for (int d = 0; d < D; ++d) {
-    const float sv = S[d * lds + lane];
+  for (int d = 0; d < D; d += 4) {   // Q's columns past D are zero, S's rows past D are never reached by a nonzero
+    float sv[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = __fmaf_rn(Q[(t_first + i) * ldq + d], sv, acc[i]);
+    for (int k = 0; k < 4; ++k) sv[k] = d + k < D ? S[(d + k) * lds + lane] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 q = *reinterpret_cast<const float4*>(Q + (t_first + i) * ldq + d);
+      acc[i] = __fmaf_rn(q.x, sv[0], acc[i]);
+      acc[i] = __fmaf_rn(q.y, sv[1], acc[i]);
+      acc[i] = __fmaf_rn(q.z, sv[2], acc[i]);
+      acc[i] = __fmaf_rn(q.w, sv[3], acc[i]);
+    }
   }
   if (lane < cols_here) {
 #pragma unroll
@@ -803,8 +827,9 @@ __global__ void __launch_bounds__(CHUNK_THREADS) matrix_memory_finish_kernel(con
 // Shared memory of the chunk kernels for heads of `dim`; 0 when they do not fit (the walk serves those).
 static size_t chunk_smem_bytes(int dim, size_t* scores_bytes, size_t* finish_bytes) {
   *scores_bytes = (2ull * CHUNK * (dim + 1) + 3 * CHUNK) * sizeof(float);
-  const size_t local = (static_cast<size_t>(CHUNK) * (dim + 1) + CHUNK * CHUNK_COLS + static_cast<size_t>(CHUNK) * (CHUNK + 1) + CHUNK) * sizeof(float);
-  *finish_bytes = (static_cast<size_t>(CHUNK) * (dim + 1) + static_cast<size_t>(dim) * (CHUNK_COLS + 1) + dim) * sizeof(float);
+  const size_t padded = (static_cast<size_t>(dim) + 3) & ~static_cast<size_t>(3);
+  const size_t local = (CHUNK * padded + CHUNK * CHUNK_COLS + static_cast<size_t>(CHUNK) * CHUNK + CHUNK) * sizeof(float);
+  *finish_bytes = (CHUNK * padded + (padded + 4) * (CHUNK_COLS + 1) + padded) * sizeof(float);
   const size_t limit = static_cast<size_t>(shrike_device().max_smem);
   return (local <= limit && *finish_bytes <= limit && *scores_bytes <= limit) ? local : 0;
 }
