@@ -60,7 +60,7 @@ VUPITAR_A = {
 # heads of 64 with one kv head (the sizes the tensor-core kernels take); the whole head rotates; no repeated layers;
 # every expert chosen and no shared expert; a limit that never clamps
 VUPITAR_B = {
-    "architecture": "Vupitar", "width": 128, "vocab": 300, "embedding": {"scale": 0.5}, "norm": {"eps": 1e-6},
+    "architecture": "Vupitar", "width": 128, "vocab": 300, "embedding": {"scale": 0.25}, "norm": {"eps": 1e-6},
     "layers": [
         _layer(_left(2, 1, 64, 64, 0.12, chunk=37, rot=(64, 1000000.0)), _right(1, 64, 64, 15.0), (1.0, 1.0), _dense(192, 7.0)),
         _layer(_left(2, 1, 64, 64, 0.12, chunk=37, rot=(64, 1000000.0)), _right(1, 64, 64, 15.0), (1.0, 1.0), _moe(3, 3, 32)),
